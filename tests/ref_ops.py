@@ -37,8 +37,144 @@ class RefOps:
         return max(1, -(-max_ctx // self.decode_split_keys))
 
     # ---- embedding: x[t] = E[token[t]] (fork.rs:935) -------------------------------
-    def embedding(self, token_ids, table, out):
-        out.copy_(table[token_ids.long()].float())
+    def embedding(self, token_ids, table, out, scale=1.0):
+        out.copy_(table[token_ids.long()].float() * scale)
+
+    def linear_plain(self, x, w, out, mode):
+        self.linear(x, w, out, mode)
+
+    # ---- Dynamic Tanh and the soft cap ---------------------------------------------------
+    def dynamic_tanh(self, x, alpha, weight, bias, out):
+        out.copy_((torch.tanh(alpha.float() * x.float()) * weight.float() + bias.float()).to(out.dtype))
+
+    def softcap(self, x, cap):
+        x.copy_(cap * torch.tanh(x / cap))
+
+    # ---- attention through a cached latent ------------------------------------------------
+    @staticmethod
+    def _rotate(v, pos, freqs):
+        """v [..., rot]: the first dims entries rotated, entry i with i + dims/2, angle pos * f_i."""
+        f, mag, dims = freqs
+        if dims == 0:
+            return v
+        half = dims // 2
+        ang = (torch.tensor(float(pos), dtype=torch.float32) * f.float().cpu())
+        c, s = torch.cos(ang) * mag, torch.sin(ang) * mag
+        a, b = v[..., :half], v[..., half:dims]
+        return torch.cat([a * c - b * s, b * c + a * s, v[..., dims:]], dim=-1)
+
+    def latent_prepare(self, proj, off_q, q_rank, off_kv, rank, rot, wq, wc, eps, freqs, cq, ctx, cache, write_cache=True):
+        bs = cache.block_size if write_cache else 1
+        for t in range(proj.shape[0]):
+            slot = int(ctx.row_slot[t])
+            if slot < 0:
+                cq[t].zero_()
+                continue
+            row = proj[t].float()
+            a = row[off_q:off_q + q_rank]
+            cq[t].copy_((a / torch.sqrt((a * a).mean() + eps) * wq.float()).to(cq.dtype))
+            if not write_cache:
+                continue
+            c = row[off_kv:off_kv + rank]
+            c = c / torch.sqrt((c * c).mean() + eps) * wc.float()
+            p = int(ctx.positions[t])
+            kr = self._rotate(row[off_kv + rank:off_kv + rank + rot], p, freqs)
+            page = int(cache.block_table[slot, p // bs])
+            assert page >= 0, "write to a position without a page"
+            cache.k_pages[page, 0, p % bs, :] = torch.cat([c, kr]).to(cache.k_pages.dtype)
+
+    def latent_attention(self, q_lat, q, q_off, out, ctx, cache, n_heads, rank, rot, freqs, scale):
+        bs = cache.block_size
+        T = q.shape[0]
+        for t in range(T):
+            slot = int(ctx.row_slot[t])
+            if slot < 0:
+                out[t].zero_()
+                continue
+            p = int(ctx.positions[t])
+            idx = torch.arange(0, p + 1)
+            pages = cache.block_table[slot, (idx // bs).long()].long()
+            assert (pages >= 0).all(), "read of a position whose page was given back"
+            rows = cache.k_pages[pages, 0, (idx % bs).long(), :].float()          # [n, rank + rot]
+            ql = q_lat[t].float().reshape(n_heads, rank)
+            qr = self._rotate(q[t].float().reshape(n_heads, q_off)[:, q_off - rot:], p, freqs)
+            sc = (ql @ rows[:, :rank].T + qr @ rows[:, rank:].T) * scale
+            out[t].copy_((torch.softmax(sc, dim=-1) @ rows[:, :rank]).reshape(-1).to(out.dtype))
+
+    def linear_heads(self, x, x_head_stride, w, out, gate=None, out_scale=1.0):
+        G, N, K = w.shape
+        for g in range(G):
+            y = x[:, g * x_head_stride:g * x_head_stride + K].float() @ w[g].float().T
+            if gate is not None:
+                gt, c0 = gate
+                y = y * torch.sigmoid(gt[:, c0 + g * N:c0 + (g + 1) * N].float()) * out_scale
+            out[:, g * N:(g + 1) * N] = y.to(out.dtype)
+
+    # ---- matrix memory ------------------------------------------------------------------------
+    @staticmethod
+    def plan_row_segments(entries, starts, aux, bucketed=False):
+        from zllm_b200.kernels.ops import CudaOps
+        return CudaOps.plan_row_segments(entries, starts, aux, bucketed)
+
+    def matrix_memory(self, qkvg, oq, ok, ov, og, z, bias_i, bias_f, cap, norm_w, eps, mult, out, ctx, cache, H, dk, dv):
+        T = qkvg.shape[0]
+        x = qkvg.float()
+        segs = ctx.aux.get("row_segments") if ctx.aux else None
+        runs = [(int(a), int(b), int(c)) for a, b, c, _ in segs.tolist()] if segs is not None else \
+            [(t, 1, int(ctx.row_slot[t])) for t in range(T)]
+        raw = torch.zeros(T, H, dv)
+        for row0, rows, slot in runs:
+            if rows <= 0 or slot < 0:
+                continue
+            st = cache.state[slot].reshape(H, dk * dv + dk + 1)
+            for h in range(H):
+                S = st[h, :dk * dv].reshape(dk, dv).clone()
+                n = st[h, dk * dv:dk * dv + dk].clone()
+                m = st[h, dk * dv + dk].clone()
+                for t in range(row0, row0 + rows):
+                    q = x[t, oq + h * dk:oq + (h + 1) * dk] * dk ** -0.5
+                    k = x[t, ok + h * dk:ok + (h + 1) * dk]
+                    v = x[t, ov + h * dv:ov + (h + 1) * dv]
+                    gi = cap * torch.tanh((z[t, h] + bias_i[h]) / cap)
+                    gf = torch.nn.functional.logsigmoid(cap * torch.tanh((z[t, H + h] + bias_f[h]) / cap))
+                    m_new = torch.maximum(gf + m, gi)
+                    keep, take = torch.exp(gf + m - m_new), torch.exp(gi - m_new)
+                    S = keep * S + take * k[:, None] * v[None, :]
+                    n = keep * n + take * k
+                    m = m_new
+                    raw[t, h] = (S.T @ q) / (torch.maximum((n * q).sum().abs(), torch.exp(-m)) + 1e-6)
+                st[h, :dk * dv] = S.reshape(-1)
+                st[h, dk * dv:dk * dv + dk] = n
+                st[h, dk * dv + dk] = m
+        y = raw / torch.sqrt((raw * raw).mean(-1, keepdim=True) + eps)
+        y = y.reshape(T, H * dv) * norm_w.float() * torch.sigmoid(x[:, og:og + H * dv]) * mult
+        live = (ctx.row_slot[:T] >= 0)[:, None]
+        out.copy_(torch.where(live, y, torch.zeros_like(y)).to(out.dtype))
+
+    # ---- mixture of experts ----------------------------------------------------------------------
+    def moe_route(self, h, w_router, top, groups, keep, idx, weights):
+        s = torch.softmax(h.float() @ w_router.float().T, dim=-1)
+        T, E = s.shape
+        per = E // groups
+        gbest = s.reshape(T, groups, per).max(-1).values
+        kept = torch.zeros(T, groups, dtype=torch.bool)
+        kept.scatter_(1, torch.topk(gbest, keep, dim=-1).indices, True)
+        masked = torch.where(kept[:, :, None].expand(T, groups, per).reshape(T, E), s, torch.full_like(s, -1.0))
+        ch = torch.topk(masked, top, dim=-1).indices
+        sc = torch.gather(s, 1, ch)
+        idx.copy_(ch.to(idx.dtype))
+        weights.copy_(sc / (sc.sum(-1, keepdim=True) + 1e-20))
+
+    def moe_experts(self, h, idx, weights, w_gate, w_up, w_down, residual, scale, ws):
+        x = h.float()
+        for t in range(x.shape[0]):
+            acc = torch.zeros(x.shape[1])
+            for j in range(idx.shape[1]):
+                e = int(idx[t, j])
+                a = x[t] @ w_gate[e].float().T
+                act = (a / (1.0 + torch.exp(-a)) * (x[t] @ w_up[e].float().T)).to(h.dtype).float()
+                acc = acc + weights[t, j] * (act @ w_down[e].float().T)
+            residual[t] += scale * acc
 
     # ---- BNORM (shaders.rs:545-564) --------------------------------------------------
     def rmsnorm(self, x, weight, eps, out, rows=None):

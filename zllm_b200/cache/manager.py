@@ -13,7 +13,7 @@ request slots are a stack, slot 0 first, kept for the request's life
 (src/backend/gpu/batch.rs:65-66).
 
 Beyond the reference (whose layers all have identical pools): layers are put
-into *groups* by what they need -- (kv heads, head size, window) -- and each
+into *groups* by what they need -- (kv heads, head size, window, value rows or not) -- and each
 group has its own pool and tables under the shared slot id.  A group with a
 window gives pages back during the request, as soon as every position of the
 page has fallen out of the window of the next query.  Per-request state of
@@ -116,7 +116,7 @@ class KVLayerView:
     """What a mixer sees of its cache: key pages, value pages, the group's table."""
 
     k_pages: torch.Tensor        # [num_pages, n_kv_heads, block_size, head_dim]
-    v_pages: torch.Tensor
+    v_pages: Optional[torch.Tensor]     # None for a cache spec without value rows
     block_table: torch.Tensor    # [max_slots, max_blocks] int32, NO_PAGE where none
     block_size: int
     window: Optional[int]
@@ -185,7 +185,7 @@ class CacheManager:
             if cache_of is not None or spec is None:
                 continue
             if isinstance(spec, KVCacheSpec):
-                key = (spec.n_kv_heads, spec.head_dim, spec.window)
+                key = (spec.n_kv_heads, spec.head_dim, spec.window, spec.values)
                 g = by_key.get(key)
                 if g is None:
                     g = KVGroup(len(self.groups), spec, self.block_size, num_pages, max_slots, max_len)
@@ -216,7 +216,8 @@ class CacheManager:
         dev = self.device
         for g in self.groups:
             s = g.spec
-            g.storage = torch.zeros((len(g.entries), 2, g.pool.num_pages, s.n_kv_heads, self.block_size, s.head_dim),
+            g.storage = torch.zeros((len(g.entries), 2 if s.values else 1, g.pool.num_pages, s.n_kv_heads, self.block_size,
+                                     s.head_dim),
                                     dtype=self.dtype, device=dev)
             g.table_dev = torch.full((self.max_slots, g.max_blocks), NO_PAGE, dtype=torch.int32, device=dev)
             g.table_pinned = torch.from_numpy(g.table)
@@ -224,8 +225,8 @@ class CacheManager:
                 g.table_pinned = torch.full((self.max_slots, g.max_blocks), NO_PAGE, dtype=torch.int32).pin_memory()
                 g.table = g.table_pinned.numpy()
             for j, ei in enumerate(g.entries):
-                self.views[ei] = KVLayerView(g.storage[j, 0], g.storage[j, 1], g.table_dev, self.block_size,
-                                             g.window, g.index)
+                self.views[ei] = KVLayerView(g.storage[j, 0], g.storage[j, 1] if s.values else None, g.table_dev,
+                                             self.block_size, g.window, g.index)
         for ei, spec in self._state_entries.items():
             t = torch.zeros((self.max_slots, *spec.shape), dtype=getattr(torch, spec.dtype), device=dev)
             self.state[ei] = t

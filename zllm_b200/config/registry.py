@@ -47,11 +47,16 @@ def known_architectures():
 
 
 def architecture_of(config_json: dict) -> ArchEntry:
-    """The entry named by ``architectures[0]`` of a raw config.json dictionary."""
+    """The entry named by ``architectures[0]`` of a raw config.json dictionary, or by its
+    ``architecture`` (one name) where a model family writes it that way."""
     archs = config_json.get("architectures")
-    if not archs or not isinstance(archs, (list, tuple)):
-        raise ConfigError("config.json: missing key 'architectures' (a list with the model class name)")
-    return architecture(archs[0])
+    if archs and isinstance(archs, (list, tuple)):
+        return architecture(archs[0])
+    one = config_json.get("architecture")
+    if isinstance(one, str) and one:
+        return architecture(one)
+    raise ConfigError("config.json: missing key 'architectures' (a list with the model class name) "
+                      "or 'architecture' (the name)")
 
 
 _plugins_loaded = False
@@ -64,7 +69,7 @@ def _ensure_builtin():
     functions, and the command line, ``bin/trace_run`` and the Python entry points then take its
     model folders like any other."""
     global _plugins_loaded
-    from ..models import llama  # noqa: F401
+    from ..models import llama, sepirax  # noqa: F401
     if not _plugins_loaded:
         _plugins_loaded = True
         import importlib

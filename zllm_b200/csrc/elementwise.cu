@@ -1,5 +1,6 @@
-// Row-wise kernels: embedding gather, RMSNorm, SiLU-mul, row gather, rotary
-// encoding fused with the write of keys and values into cache pages.
+// Row-wise kernels: embedding gather (with a scale), RMSNorm, Dynamic Tanh, SiLU-mul, row
+// gather, the soft cap of logits, rotary encoding fused with the write of keys and values
+// into cache pages.
 //
 // Counterparts in zllm (WGSL, src/backend/gpu/shaders.rs): BNORM 545-564, BROPE
 // 566-587, BKV_PACK 727-756, SILU_MUL 976-990; the embedding gather is done on
@@ -11,7 +12,7 @@
 // ---------------------------------------------------------------- embedding
 template <typename WT>
 __global__ void embedding_kernel(const int* tok, const WT* __restrict__ table, float* out,
-                                 int H, int V) {
+                                 int H, int V, float scale) {
     pdl_trigger();
     pdl_wait();
     const int t = blockIdx.x;
@@ -22,15 +23,16 @@ __global__ void embedding_kernel(const int* tok, const WT* __restrict__ table, f
         return;
     }
     const WT* row = table + (size_t)id * H;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = to_f32(row[i]);
+    for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = to_f32(row[i]) * scale;
 }
 
+// out[t] = table[tok[t]] * scale (scale 1 leaves the values as they are)
 ZLLM_API int zllm_embedding(const int* tok, const void* table, float* out, int T, int H, int V, int table_bf16,
-                            void* stream) {
+                            float scale, void* stream) {
     if (T <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
-    if (table_bf16) return launch_pdl(embedding_kernel<bf16>, dim3(T), dim3(256), 0, s, tok, (const bf16*)table, out, H, V);
-    return launch_pdl(embedding_kernel<float>, dim3(T), dim3(256), 0, s, tok, (const float*)table, out, H, V);
+    if (table_bf16) return launch_pdl(embedding_kernel<bf16>, dim3(T), dim3(256), 0, s, tok, (const bf16*)table, out, H, V, scale);
+    return launch_pdl(embedding_kernel<float>, dim3(T), dim3(256), 0, s, tok, (const float*)table, out, H, V, scale);
 }
 
 // ---------------------------------------------------------------- rmsnorm
@@ -120,6 +122,47 @@ ZLLM_API int zllm_rmsnorm(const float* x, const int* rows, const void* w, void* 
     if (w_bf16) return launch_rmsnorm<bf16, float>(x, rows, w, y, T, H, eps, s);
     if (out_bf16) return launch_rmsnorm<float, bf16>(x, rows, w, y, T, H, eps, s);
     return launch_rmsnorm<float, float>(x, rows, w, y, T, H, eps, s);
+}
+
+// ---------------------------------------------------------------- dynamic tanh
+// y = tanh(alpha * x) * w + b, element by element: a norm that takes no statistics of the row.
+// x float32 [T,H]; alpha (one value on the device), w and b float32; y AT.
+template <typename OT>
+__global__ void dynamic_tanh_kernel(const float* x, const float* __restrict__ alpha, const float* __restrict__ w,
+                                    const float* __restrict__ b, OT* y, int H, size_t n) {
+    pdl_trigger();
+    const float a = alpha[0];
+    pdl_wait();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) {
+        const int c = (int)(i % (size_t)H);
+        y[i] = from_f32<OT>(tanhf(a * x[i]) * w[c] + b[c]);
+    }
+}
+
+ZLLM_API int zllm_dynamic_tanh(const float* x, const float* alpha, const float* w, const float* b, void* y, int T, int H,
+                               int out_bf16, void* stream) {
+    if (T <= 0) return 0;
+    const size_t n = (size_t)T * H;
+    const unsigned blocks = (unsigned)((n + 255) / 256);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (out_bf16) return launch_pdl(dynamic_tanh_kernel<bf16>, dim3(blocks), dim3(256), 0, s, x, alpha, w, b, (bf16*)y, H, n);
+    return launch_pdl(dynamic_tanh_kernel<float>, dim3(blocks), dim3(256), 0, s, x, alpha, w, b, (float*)y, H, n);
+}
+
+// ---------------------------------------------------------------- soft cap
+// x <- cap * tanh(x / cap), in place, float32 (logits before sampling).
+__global__ void softcap_kernel(float* x, float cap, size_t n) {
+    pdl_trigger();
+    pdl_wait();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) x[i] = cap * tanhf(x[i] / cap);
+}
+
+ZLLM_API int zllm_softcap(float* x, long long n, float cap, void* stream) {
+    if (n <= 0) return 0;
+    if (!(cap > 0.f)) return ZLLM_ERR_UNSUPPORTED;
+    return launch_pdl(softcap_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, (cudaStream_t)stream, x, cap, (size_t)n);
 }
 
 // ---------------------------------------------------------------- silu * up

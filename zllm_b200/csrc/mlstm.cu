@@ -1,0 +1,221 @@
+// A matrix memory with exponential gates (mLSTM): per request and head a matrix S [dk, dv], a
+// vector n [dk] and a running maximum m of the accumulated log gates, all float32, carried
+// from token to token in the request's state slot.
+//
+//   gi = cap tanh((zi + bi) / cap)                     log input gate
+//   gf = logsigmoid(cap tanh((zf + bf) / cap))         log forget gate
+//   m' = max(gf + m, gi);  keep = exp(gf + m - m');  take = exp(gi - m')
+//   S' = keep S + take k v^T;   n' = keep n + take k
+//   out = S'^T q / (max(|n' . q|, exp(-m')) + 1e-6),   q already times dk^(-1/2)
+//
+// Three kernels per step of the engine:
+//   mlstm_gates:  one warp per (segment, head) walks the segment's tokens in order: gates, m,
+//                 n and n.q; leaves (keep, take, denominator) per (row, head) and the new n, m.
+//   mlstm_scan:   blocks per (segment, head, slice of dv): each thread owns part of one column
+//                 of S in registers and walks the tokens in order; q, k, v and the per-token
+//                 factors come through shared memory eight tokens at a time.
+//   mlstm_finish: per row and head: out / rms(out), times the norm weight, the output gate
+//                 sigmoid(g) and a constant.
+// A segment is the run of a request's rows in the step, (first row, rows, slot, ...), from a
+// table the host wrote; without a table every row is a segment of its own (decode steps) and
+// its slot is row_slot[row].  Segments with no rows or a negative slot are skipped.
+// State of a slot: per head [S (dk*dv) | n (dk) | m].
+#include "common.cuh"
+#include <math.h>
+
+#define ML_NL 16          // n entries per lane: dk <= 512
+#define ML_CHUNK 8        // tokens staged at a time by the scan
+#define ML_COLT 128       // threads of a scan block
+
+__device__ __forceinline__ bool segment_of(const int* segs, const int* row_slot, int s, int& row0, int& rows, int& slot) {
+    if (segs != nullptr) {
+        row0 = segs[4 * s]; rows = segs[4 * s + 1]; slot = segs[4 * s + 2];
+    } else {
+        row0 = s; rows = 1; slot = row_slot[s];
+    }
+    return rows > 0 && slot >= 0;
+}
+
+template <typename AT>
+__global__ void __launch_bounds__(32) mlstm_gates_kernel(
+    const AT* qkv, int ld, int oq, int ok, const float* z, const float* __restrict__ bi, const float* __restrict__ bf,
+    float cap, float qscale, const int* __restrict__ segs, const int* row_slot, float* state, size_t state_stride,
+    float* fac, int H, int dk, int dv) {
+    pdl_trigger();
+    pdl_wait();
+    const int h = blockIdx.y, lane = threadIdx.x;
+    int row0, rows, slot;
+    if (!segment_of(segs, row_slot, blockIdx.x, row0, rows, slot)) return;
+    float* st = state + (size_t)slot * state_stride + (size_t)h * ((size_t)dk * dv + dk + 1);
+    float* np = st + (size_t)dk * dv;
+    float n[ML_NL];
+#pragma unroll
+    for (int i = 0; i < ML_NL; ++i) { const int r = lane + 32 * i; n[i] = r < dk ? np[r] : 0.f; }
+    float m = np[dk];
+    const float b_i = bi[h], b_f = bf[h];
+    for (int t = row0; t < row0 + rows; ++t) {
+        const float zi = z[(size_t)t * 2 * H + h], zf = z[(size_t)t * 2 * H + H + h];
+        const float gi = cap * tanhf((zi + b_i) / cap);
+        const float a = cap * tanhf((zf + b_f) / cap);
+        const float gf = fminf(a, 0.f) - log1pf(expf(-fabsf(a)));
+        const float m_new = fmaxf(gf + m, gi);
+        const float keep = expf(gf + m - m_new), take = expf(gi - m_new);
+        const AT* qr = qkv + (size_t)t * ld + oq + (size_t)h * dk;
+        const AT* kr = qkv + (size_t)t * ld + ok + (size_t)h * dk;
+        float dot = 0.f;
+#pragma unroll
+        for (int i = 0; i < ML_NL; ++i) {
+            const int r = lane + 32 * i;
+            if (r < dk) {
+                n[i] = keep * n[i] + take * to_f32(kr[r]);
+                dot = fmaf(n[i], to_f32(qr[r]) * qscale, dot);
+            }
+        }
+        dot = warp_sum(dot);
+        m = m_new;
+        if (lane == 0) {
+            float* f = fac + ((size_t)t * H + h) * 4;
+            f[0] = keep; f[1] = take; f[2] = fmaxf(fabsf(dot), expf(-m)) + 1e-6f;
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < ML_NL; ++i) { const int r = lane + 32 * i; if (r < dk) np[r] = n[i]; }
+    if (lane == 0) np[dk] = m;
+}
+
+template <typename AT, int RPT>     // RPT: rows of S per thread
+__global__ void __launch_bounds__(ML_COLT) mlstm_scan_kernel(
+    const AT* qkv, int ld, int oq, int ok, int ov, const float* fac, float qscale, const int* __restrict__ segs,
+    const int* row_slot, float* state, size_t state_stride, float* out, int H, int dk, int dv, int kp) {
+    extern __shared__ float sm[];
+    pdl_trigger();
+    pdl_wait();
+    const int h = blockIdx.y;
+    int row0, rows, slot;
+    if (!segment_of(segs, row_slot, blockIdx.x, row0, rows, slot)) return;
+    const int vs = ML_COLT / kp;                      // columns of this block
+    const int sub = threadIdx.x % kp;                 // which rows of the column: sub, sub + kp, ...
+    const int col = blockIdx.z * vs + threadIdx.x / kp;
+    const bool has = col < dv;
+    float* S = state + (size_t)slot * state_stride + (size_t)h * ((size_t)dk * dv + dk + 1);
+    float s[RPT];
+#pragma unroll
+    for (int i = 0; i < RPT; ++i) { const int r = sub + i * kp; s[i] = (has && r < dk) ? S[(size_t)r * dv + col] : 0.f; }
+    const int per = 2 * dk + vs + 4;                  // floats staged per token: q, k, v slice, factors
+    for (int c0 = 0; c0 < rows; c0 += ML_CHUNK) {
+        const int nc = min(ML_CHUNK, rows - c0);
+        __syncthreads();
+        for (int i = threadIdx.x; i < nc * per; i += ML_COLT) {
+            const int j = i / per, e = i - j * per;
+            const size_t t = (size_t)(row0 + c0 + j);
+            float v;
+            if (e < dk) v = to_f32(qkv[t * ld + oq + (size_t)h * dk + e]) * qscale;
+            else if (e < 2 * dk) v = to_f32(qkv[t * ld + ok + (size_t)h * dk + (e - dk)]);
+            else if (e < 2 * dk + vs) {
+                const int cc = blockIdx.z * vs + (e - 2 * dk);
+                v = cc < dv ? to_f32(qkv[t * ld + ov + (size_t)h * dv + cc]) : 0.f;
+            } else v = fac[(t * H + h) * 4 + (e - 2 * dk - vs)];
+            sm[i] = v;
+        }
+        __syncthreads();
+        for (int j = 0; j < nc; ++j) {
+            const float* q = sm + j * per;
+            const float* k = q + dk;
+            const float vv = q[2 * dk + threadIdx.x / kp];
+            const float keep = q[2 * dk + vs], take = q[2 * dk + vs + 1], den = q[2 * dk + vs + 2];
+            const float tv = take * vv;
+            float num = 0.f;
+#pragma unroll
+            for (int i = 0; i < RPT; ++i) {
+                const int r = sub + i * kp;
+                if (r < dk) {
+                    s[i] = fmaf(tv, k[r], keep * s[i]);
+                    num = fmaf(s[i], q[r], num);
+                }
+            }
+            for (int o = 1; o < kp; o <<= 1) num += __shfl_xor_sync(0xffffffffu, num, o);
+            if (has && sub == 0) out[(size_t)(row0 + c0 + j) * H * dv + (size_t)h * dv + col] = num / den;
+        }
+    }
+    if (has) {
+#pragma unroll
+        for (int i = 0; i < RPT; ++i) { const int r = sub + i * kp; if (r < dk) S[(size_t)r * dv + col] = s[i]; }
+    }
+}
+
+template <typename AT>
+__global__ void __launch_bounds__(256) mlstm_finish_kernel(const float* raw, const AT* gate, int ldg, int og,
+                                                           const float* __restrict__ w, AT* out, const int* row_slot, int H,
+                                                           int dv, float eps, float mult) {
+    pdl_trigger();
+    pdl_wait();
+    const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+    const bool pad = row_slot[t] < 0;
+    for (int h = warp; h < H; h += nw) {
+        const float* r = raw + ((size_t)t * H + h) * dv;
+        AT* o = out + ((size_t)t * H + h) * dv;
+        if (pad) {
+            for (int c = lane; c < dv; c += 32) o[c] = from_f32<AT>(0.f);
+            continue;
+        }
+        float ss = 0.f;
+        for (int c = lane; c < dv; c += 32) ss += r[c] * r[c];
+        ss = warp_sum(ss);
+        const float inv = 1.f / sqrtf(ss / (float)dv + eps);
+        for (int c = lane; c < dv; c += 32) {
+            const float g = to_f32(gate[(size_t)t * ldg + og + (size_t)h * dv + c]);
+            o[c] = from_f32<AT>(r[c] * inv * w[h * dv + c] * (1.f / (1.f + expf(-g))) * mult);
+        }
+    }
+}
+
+// qkv [T, ld]: head h's queries at column oq + h*dk, keys at ok + h*dk, values at ov + h*dv,
+// output-gate inputs at og + h*dv.  z [T, 2H] float32: the input gates' then the forget gates'
+// projections.  fac [T, H, 4] and raw [T, H*dv] float32 are scratch; out [T, H*dv] receives
+// the gated, normed result.  segs: null or [n_seg, 4].
+ZLLM_API int zllm_mlstm(const void* qkv, int ld, int oq, int ok, int ov, int og, const float* z, const float* bi,
+                        const float* bf, float cap, const float* wnorm, float eps, float mult, const int* segs, int n_seg,
+                        const int* row_slot, float* state, long long state_stride, float* fac, float* raw, void* out, int T,
+                        int H, int dk, int dv, int is_bf16, void* stream) {
+    if (T <= 0) return 0;
+    if (dk <= 0 || dk > 32 * ML_NL || dv <= 0 || H <= 0 || !(cap > 0.f)) return ZLLM_ERR_UNSUPPORTED;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int ns = segs != nullptr ? n_seg : T;
+    const float qscale = 1.f / sqrtf((float)dk);
+    int kp = 1;
+    while (kp * 64 < dk) kp *= 2;                     // rows per thread <= 64
+    const int rpt = (dk + kp - 1) / kp;
+    const int vs = ML_COLT / kp;
+    const size_t smem = (size_t)ML_CHUNK * (2 * dk + vs + 4) * sizeof(float);
+    dim3 grid(ns, H, (dv + vs - 1) / vs);
+    int code;
+    if (ns > 0) {
+        if (is_bf16) {
+            code = launch_pdl(mlstm_gates_kernel<bf16>, dim3(ns, H), dim3(32), 0, s, (const bf16*)qkv, ld, oq, ok, z, bi, bf, cap,
+                              qscale, segs, row_slot, state, (size_t)state_stride, fac, H, dk, dv);
+            if (code) return code;
+            if (rpt <= 32)
+                code = launch_pdl(mlstm_scan_kernel<bf16, 32>, grid, dim3(ML_COLT), smem, s, (const bf16*)qkv, ld, oq, ok, ov, fac,
+                                  qscale, segs, row_slot, state, (size_t)state_stride, raw, H, dk, dv, kp);
+            else
+                code = launch_pdl(mlstm_scan_kernel<bf16, 64>, grid, dim3(ML_COLT), smem, s, (const bf16*)qkv, ld, oq, ok, ov, fac,
+                                  qscale, segs, row_slot, state, (size_t)state_stride, raw, H, dk, dv, kp);
+        } else {
+            code = launch_pdl(mlstm_gates_kernel<float>, dim3(ns, H), dim3(32), 0, s, (const float*)qkv, ld, oq, ok, z, bi, bf,
+                              cap, qscale, segs, row_slot, state, (size_t)state_stride, fac, H, dk, dv);
+            if (code) return code;
+            if (rpt <= 32)
+                code = launch_pdl(mlstm_scan_kernel<float, 32>, grid, dim3(ML_COLT), smem, s, (const float*)qkv, ld, oq, ok, ov,
+                                  fac, qscale, segs, row_slot, state, (size_t)state_stride, raw, H, dk, dv, kp);
+            else
+                code = launch_pdl(mlstm_scan_kernel<float, 64>, grid, dim3(ML_COLT), smem, s, (const float*)qkv, ld, oq, ok, ov,
+                                  fac, qscale, segs, row_slot, state, (size_t)state_stride, raw, H, dk, dv, kp);
+        }
+        if (code) return code;
+    }
+    if (is_bf16)
+        return launch_pdl(mlstm_finish_kernel<bf16>, dim3(T), dim3(256), 0, s, raw, (const bf16*)qkv, ld, og, wnorm, (bf16*)out,
+                          row_slot, H, dv, eps, mult);
+    return launch_pdl(mlstm_finish_kernel<float>, dim3(T), dim3(256), 0, s, raw, (const float*)qkv, ld, og, wnorm, (float*)out,
+                      row_slot, H, dv, eps, mult);
+}

@@ -1,0 +1,149 @@
+// Routing of a mixture of experts: router scores, the choice of experts, the sorting of
+// (token, choice) pairs by expert, and the weighted sum of the experts' outputs.
+//
+//   moe_route:    z = Wr h in float32, s = softmax(z) over all E experts.  Experts form
+//                 ``groups`` equal groups of neighbours; a group counts by its largest score;
+//                 only experts of the ``keep`` best groups can be chosen (groups = keep = 1: no
+//                 restriction).  The ``top`` largest scores among those are chosen, lowest index
+//                 first on ties; their weights are the scores divided by their sum (+ 1e-20).
+//   moe_sort:     a counting sort of the T*top pairs by expert: off[E+1], perm[T*top].
+//   moe_combine:  residual[t] += scale * sum_j weight[t][j] * y[t*top + j], j in order.
+#include "common.cuh"
+#include <math.h>
+
+#define MOE_MAX_E 1024
+
+template <typename AT>
+__global__ void __launch_bounds__(256) moe_route_kernel(const AT* h, const AT* __restrict__ wr, int* idx, float* wt, int H,
+                                                        int E, int top, int groups, int keep) {
+    __shared__ float sc[MOE_MAX_E];
+    __shared__ float gs[MOE_MAX_E];
+    pdl_trigger();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+    const AT* hr = h + (size_t)t * H;
+    for (int e = warp; e < E; e += nw) {
+        const AT* w = wr + (size_t)e * H;
+        float dot = 0.f;
+        for (int i = lane; i < H; i += 32) dot = fmaf(to_f32(hr[i]), to_f32(w[i]), dot);
+        dot = warp_sum(dot);
+        if (lane == 0) sc[e] = dot;
+    }
+    __syncthreads();
+    if (warp != 0) return;
+    // softmax over the experts
+    float mx = -INFINITY;
+    for (int e = lane; e < E; e += 32) mx = fmaxf(mx, sc[e]);
+    mx = warp_max(mx);
+    float sum = 0.f;
+    for (int e = lane; e < E; e += 32) { const float p = expf(sc[e] - mx); sc[e] = p; sum += p; }
+    sum = warp_sum(sum);
+    __syncwarp();
+    for (int e = lane; e < E; e += 32) sc[e] = sc[e] / sum;
+    __syncwarp();
+    // groups: the best ``keep`` by their largest score; the others' experts are struck out
+    const int per = E / groups;
+    if (groups > 1 && keep < groups) {
+        for (int g = lane; g < groups; g += 32) {
+            float b = -1.f;
+            for (int i = 0; i < per; ++i) b = fmaxf(b, sc[g * per + i]);
+            gs[g] = b;
+        }
+        __syncwarp();
+        // a group stays if fewer than ``keep`` groups beat it (lower index wins a tie)
+        for (int g = lane; g < groups; g += 32) {
+            const float mine = gs[g];
+            int better = 0;
+            for (int o = 0; o < groups; ++o) better += (gs[o] > mine) || (gs[o] == mine && o < g);
+            if (better >= keep)
+                for (int i = 0; i < per; ++i) sc[g * per + i] = -2.f - sc[g * per + i];   // struck out, value kept
+        }
+        __syncwarp();
+    }
+    // the ``top`` largest allowed scores, one at a time (a NaN score is never chosen; if nothing
+    // is left the lowest free index is taken so that the list always names valid experts)
+    float total = 0.f;
+    for (int j = 0; j < top; ++j) {
+        float bv = -INFINITY;
+        int bi = 0x7fffffff;
+        for (int e = lane; e < E; e += 32) {
+            const float v = sc[e];
+            if (v >= 0.f && (v > bv || (v == bv && e < bi))) { bv = v; bi = e; }
+        }
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+        }
+        if (bi == 0x7fffffff) { bi = j < E ? j : 0; bv = 0.f; }
+        if (lane == 0) {
+            idx[(size_t)t * top + j] = bi;
+            wt[(size_t)t * top + j] = bv;
+            sc[bi] = -1.f;
+        }
+        total += bv;
+        __syncwarp();
+    }
+    const float inv = 1.f / (total + 1e-20f);
+    for (int j = lane; j < top; j += 32) wt[(size_t)t * top + j] *= inv;
+}
+
+ZLLM_API int zllm_moe_route(const void* h, const void* wr, int* idx, float* wt, int T, int H, int E, int top, int groups,
+                            int keep, int is_bf16, void* stream) {
+    if (T <= 0) return 0;
+    if (E <= 0 || E > MOE_MAX_E || top <= 0 || top > E || groups <= 0 || E % groups || keep <= 0 || keep > groups ||
+        top > keep * (E / groups))
+        return ZLLM_ERR_UNSUPPORTED;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (is_bf16)
+        return launch_pdl(moe_route_kernel<bf16>, dim3(T), dim3(256), 0, s, (const bf16*)h, (const bf16*)wr, idx, wt, H, E, top,
+                          groups, keep);
+    return launch_pdl(moe_route_kernel<float>, dim3(T), dim3(256), 0, s, (const float*)h, (const float*)wr, idx, wt, H, E, top,
+                      groups, keep);
+}
+
+// One block.  The order of pairs inside an expert's range depends on the atomics; no result
+// does, since every pair's outputs are computed from its own row alone.
+__global__ void __launch_bounds__(1024) moe_sort_kernel(const int* idx, int* off, int* perm, int n, int E) {
+    __shared__ int cnt[MOE_MAX_E + 1];
+    __shared__ int cur[MOE_MAX_E];
+    pdl_trigger();
+    pdl_wait();
+    for (int e = threadIdx.x; e <= E; e += blockDim.x) cnt[e] = 0;
+    __syncthreads();
+    for (int i = threadIdx.x; i < n; i += blockDim.x) atomicAdd(&cnt[min(max(idx[i], 0), E - 1)], 1);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int run = 0;
+        for (int e = 0; e < E; ++e) { const int c = cnt[e]; cnt[e] = run; cur[e] = run; run += c; }
+        cnt[E] = run;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e <= E; e += blockDim.x) off[e] = cnt[e];
+    for (int i = threadIdx.x; i < n; i += blockDim.x) perm[atomicAdd(&cur[min(max(idx[i], 0), E - 1)], 1)] = i;
+}
+
+ZLLM_API int zllm_moe_sort(const int* idx, int* off, int* perm, int n_pairs, int E, void* stream) {
+    if (n_pairs <= 0) return 0;
+    if (E <= 0 || E > MOE_MAX_E) return ZLLM_ERR_UNSUPPORTED;
+    return launch_pdl(moe_sort_kernel, dim3(1), dim3(1024), 0, (cudaStream_t)stream, idx, off, perm, n_pairs, E);
+}
+
+__global__ void __launch_bounds__(256) moe_combine_kernel(const float* y, const float* wt, float* residual, int H, int top,
+                                                          float scale) {
+    pdl_trigger();
+    pdl_wait();
+    const int t = blockIdx.x;
+    for (int c = threadIdx.x; c < H; c += blockDim.x) {
+        float s = 0.f;
+        for (int j = 0; j < top; ++j) s = fmaf(wt[(size_t)t * top + j], y[((size_t)t * top + j) * H + c], s);
+        residual[(size_t)t * H + c] += scale * s;
+    }
+}
+
+ZLLM_API int zllm_moe_combine(const float* y, const float* wt, float* residual, int T, int H, int top, float scale,
+                              void* stream) {
+    if (T <= 0) return 0;
+    return launch_pdl(moe_combine_kernel, dim3(T), dim3(256), 0, (cudaStream_t)stream, y, wt, residual, H, top, scale);
+}

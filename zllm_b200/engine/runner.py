@@ -87,8 +87,13 @@ class ModelRunner:
         self.model.load_weights(tensors)
         del tensors
 
-        self.max_len = min(self.ecfg.max_model_len or self.spec.max_position, self.spec.max_position)
         bs = self.ecfg.block_size
+        if self.spec.max_position is None:
+            # the model sets no largest position: the engine's own limit, else what the pool holds,
+            # else a default
+            self.max_len = self.ecfg.max_model_len or (self.ecfg.num_blocks * bs if self.ecfg.num_blocks else self.UNBOUNDED_LEN)
+        else:
+            self.max_len = min(self.ecfg.max_model_len or self.spec.max_position, self.spec.max_position)
         needs = self.model.cache_needs()
         num_blocks = self.ecfg.num_blocks
         if num_blocks is None:
@@ -116,6 +121,8 @@ class ModelRunner:
         self.steps = 0
         self.tokens_run = 0
 
+    UNBOUNDED_LEN = 8192        # sequence limit for a model without one when the engine is given none
+
     # ------------------------------------------------------------------
     def _blocks_that_fit(self, needs, bs) -> int:
         if self.device.type != "cuda":
@@ -124,7 +131,7 @@ class ModelRunner:
         el = 2 if self.dtype == torch.bfloat16 else 4
         for spec, cache_of in needs:
             if cache_of is None and spec is not None and hasattr(spec, "n_kv_heads"):
-                per_block += 2 * bs * spec.n_kv_heads * spec.head_dim * el
+                per_block += (2 if getattr(spec, "values", True) else 1) * bs * spec.n_kv_heads * spec.head_dim * el
         if per_block == 0:
             return 1
         free, _ = torch.cuda.mem_get_info(self.device)

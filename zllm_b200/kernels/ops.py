@@ -66,7 +66,8 @@ class CudaOps:
     # since the last call.  Steps then run without CUDA graphs (events cannot be timed inside a
     # capture), so the shares are those of serialised launches, as a profiler would show them.
     PROFILED = ("embedding", "rmsnorm", "linear", "linear_normed", "qkv_rope_store", "rope_kv_store", "paged_attention",
-                "silu_mul", "gather_rows", "sample", "topk", "pool_draw", "advance_decode")
+                "silu_mul", "gather_rows", "sample", "topk", "pool_draw", "advance_decode", "dynamic_tanh", "softcap",
+                "latent_prepare", "latent_attention", "linear_heads", "matrix_memory", "moe_route", "moe_experts")
 
     def _profile_setup(self):
         self._prof_depth = 0
@@ -134,6 +135,15 @@ class CudaOps:
             lib = self._libs[name] = build.load(name)
         return lib
 
+    def prepare(self, names):
+        """Build (in parallel) and load the kernel groups a part says it will use, so that a model
+        compiles what it needs when it is made and not inside its first step."""
+        names = [n for n in names if n not in self._libs]
+        if names:
+            build.build(names)
+            for n in names:
+                self._libs[n] = build.load(n)
+
     def _stream(self):
         if self._bound_stream is not None:
             return self._bound_stream
@@ -167,7 +177,8 @@ class CudaOps:
         return max(1, -(-int(max_ctx) // self.decode_split_keys))
 
     # ---- embedding -----------------------------------------------------
-    def embedding(self, token_ids, table, out):
+    def embedding(self, token_ids, table, out, scale: float = 1.0):
+        """out[t] = table[token_ids[t]] * scale, float32."""
         self._dev(token_ids, table, out)
         T, H = out.shape
         V = table.shape[0]
@@ -175,7 +186,8 @@ class CudaOps:
                 or token_ids.numel() != T:
             raise BackendError("embedding: bad operand types or shapes")
         code = self.lib("elementwise").zllm_embedding(_ptr(token_ids), _ptr(table), _ptr(out), c_int(T), c_int(H),
-                                                      c_int(V), c_int(table.dtype == torch.bfloat16), self._stream())
+                                                      c_int(V), c_int(table.dtype == torch.bfloat16), c_float(scale),
+                                                      self._stream())
         self._check(code, "embedding")
 
     # ---- rmsnorm -------------------------------------------------------
@@ -429,6 +441,180 @@ class CudaOps:
         code = getattr(self.lib(family), prefix + "_test_hook")(ctypes.c_uint(limit), c_int(1 if skip_loads else 0))
         if code != 0:
             raise BackendError(f"{family}: test hook failed (CUDA error {code})")
+
+    # ---- dynamic tanh, soft cap ------------------------------------------
+    def dynamic_tanh(self, x, alpha, weight, bias, out):
+        """out = tanh(alpha x) * weight + bias; x float32, alpha a one-element float32 tensor."""
+        self._dev(x, alpha, weight, bias, out)
+        T, H = out.shape
+        if x.dtype != torch.float32 or tuple(x.shape) != (T, H) or weight.numel() != H or bias.numel() != H \
+                or alpha.numel() != 1 or any(t.dtype != torch.float32 for t in (alpha, weight, bias)) \
+                or out.dtype not in (torch.float32, torch.bfloat16):
+            raise BackendError("dynamic_tanh: bad operand types or shapes")
+        code = self.lib("elementwise").zllm_dynamic_tanh(_ptr(x), _ptr(alpha), _ptr(weight), _ptr(bias), _ptr(out), c_int(T),
+                                                         c_int(H), c_int(out.dtype == torch.bfloat16), self._stream())
+        self._check(code, "dynamic_tanh")
+
+    def softcap(self, x, cap: float):
+        """x <- cap tanh(x / cap) in place (float32)."""
+        self._dev(x)
+        if x.dtype != torch.float32 or not cap > 0:
+            raise BackendError("softcap: float32 values and a positive cap")
+        code = self.lib("elementwise").zllm_softcap(_ptr(x), c_longlong(x.numel()), c_float(cap), self._stream())
+        self._check(code, "softcap")
+
+    # ---- attention through a latent ----------------------------------------
+    def _check_latent_cache(self, cache, width, dtype, what):
+        self._dev(cache.k_pages, cache.block_table)
+        if cache.k_pages.dtype != dtype or tuple(cache.k_pages.shape[1:]) != (1, cache.block_size, width) \
+                or cache.block_table.dtype != torch.int32:
+            raise BackendError(f"{what}: cache pages {tuple(cache.k_pages.shape)} {cache.k_pages.dtype} do not match "
+                               f"rows of {width} entries, block {cache.block_size}, {dtype}")
+
+    def latent_prepare(self, proj, off_q, q_rank, off_kv, rank, rot, wq, wc, eps, freqs, cq, ctx, cache, write_cache=True):
+        """From the stacked down-projections ``proj``: cq = rmsnorm(query latent) * wq; the row's
+        cache entry [rmsnorm(latent) * wc | rotated key part] written to its page.
+        freqs = (frequencies [dims/2] float32 on the device, magnitude, dims)."""
+        self._dev(proj, wq, wc, freqs[0], cq, ctx.positions, ctx.row_slot)
+        T = proj.shape[0]
+        if cq.dtype != proj.dtype or tuple(cq.shape) != (T, q_rank) or wq.numel() != q_rank or wc.numel() != rank \
+                or max(off_q + q_rank, off_kv + rank + rot) > proj.shape[1] or freqs[0].numel() * 2 != freqs[2] \
+                or ctx.positions.numel() != T:
+            raise BackendError("latent_prepare: bad operand types or shapes")
+        if write_cache:
+            self._check_latent_cache(cache, rank + rot, proj.dtype, "latent_prepare")
+        code = self.lib("latent_attention").zllm_latent_prepare(
+            _ptr(proj), c_int(proj.shape[1]), c_int(off_q), c_int(q_rank), c_int(off_kv), c_int(rank), c_int(rot), _ptr(wq),
+            _ptr(wc), c_float(eps), _ptr(freqs[0]), c_float(freqs[1]), c_int(freqs[2]), _ptr(ctx.positions),
+            _ptr(ctx.row_slot), _ptr(cq), _ptr(cache.k_pages if write_cache else None),
+            _ptr(cache.block_table if write_cache else None), c_int(cache.block_table.shape[1] if write_cache else 1),
+            c_int(cache.block_size if write_cache else 1), c_int(1 if write_cache else 0), c_int(T),
+            c_int(proj.dtype == torch.bfloat16), self._stream())
+        self._check(code, "latent_prepare")
+
+    def latent_attention(self, q_lat, q, q_off, out, ctx, cache, n_heads, rank, rot, freqs, scale):
+        """out[t, h] = sum_j softmax_j(scale (q_lat[t, h] . c_j + rotated(q[t, h, -rot:]) . kr_j)) c_j over
+        the cached positions j <= the row's own, [c_j | kr_j] being the cache rows."""
+        self._dev(q_lat, q, out, ctx.positions, ctx.row_slot)
+        T = q.shape[0]
+        if q_lat.dtype != torch.float32 or tuple(q_lat.shape) != (T, n_heads * rank) or tuple(out.shape) != (T, n_heads * rank) \
+                or out.dtype != q.dtype or q.shape[1] != n_heads * q_off:
+            raise BackendError("latent_attention: bad operand types or shapes")
+        self._check_latent_cache(cache, rank + rot, q.dtype, "latent_attention")
+        code = self.lib("latent_attention").zllm_latent_attention(
+            _ptr(q_lat), _ptr(q), c_int(q.shape[1]), c_int(q_off), _ptr(out), _ptr(ctx.positions), _ptr(ctx.row_slot),
+            _ptr(cache.k_pages), _ptr(cache.block_table), c_int(cache.block_table.shape[1]), c_int(cache.block_size), c_int(T),
+            c_int(n_heads), c_int(rank), c_int(rot), _ptr(freqs[0]), c_float(freqs[1]), c_int(freqs[2]), c_float(scale),
+            c_int(q.dtype == torch.bfloat16), self._stream())
+        self._check(code, "latent_attention")
+
+    def linear_heads(self, x, x_head_stride, w, out, gate=None, out_scale: float = 1.0):
+        """Per head g: out[:, g*N:(g+1)*N] = x[:, g*stride : g*stride + K] w[g]^T with w [G, N, K];
+        with ``gate`` = (tensor [T, >= c + G*N], first column c) the result is multiplied by
+        sigmoid(gate) * out_scale."""
+        self._dev(x, w, out, gate[0] if gate is not None else None)
+        G, N, K = w.shape
+        T = x.shape[0]
+        gptr, ldg = c_void_p(0), 0
+        if gate is not None:
+            gt, c0 = gate
+            if gt.dtype != x.dtype or gt.shape[0] != T or c0 < 0 or c0 + G * N > gt.shape[1]:
+                raise BackendError("linear_heads: the gate does not match the output")
+            gptr, ldg = c_void_p(gt.data_ptr() + c0 * gt.element_size()), gt.shape[1]
+        if tuple(out.shape) != (T, G * N) or (G - 1) * x_head_stride + K > x.shape[1] \
+                or x.dtype not in (w.dtype, torch.float32) or out.dtype not in (w.dtype, torch.float32):
+            raise BackendError("linear_heads: bad operand types or shapes")
+        code = self.lib("gemm_grouped").zllm_gemm_heads(
+            _ptr(x), c_int(x.shape[1]), c_int(x_head_stride), _ptr(w), _ptr(out), gptr, c_int(ldg), c_float(out_scale), c_int(T),
+            c_int(N), c_int(K), c_int(G), c_int(w.dtype == torch.bfloat16), c_int(x.dtype == torch.float32),
+            c_int(out.dtype == torch.float32), self._stream())
+        self._check(code, "gemm_heads")
+
+    # ---- matrix memory (mLSTM) -----------------------------------------------
+    @staticmethod
+    def plan_row_segments(entries, starts, aux, bucketed=False):
+        """A step planner for mixers with per-request state: every entry's run of rows as
+        [first row, rows, slot, position of the first row].  ``bucketed``: the list is rounded up
+        to a power of two with empty segments, which the kernels skip."""
+        n_real = len(entries)
+        n = n_real
+        if bucketed:
+            n = 1
+            while n < n_real:
+                n *= 2
+        host, off = aux.take(4 * n)
+        host[4 * n_real:4 * n] = (0, 0, -1, 0) * (n - n_real)
+        r = 0
+        for i, (e, start) in enumerate(zip(entries, starts)):
+            m = len(e.tokens)
+            host[4 * i:4 * i + 4] = (r, m, e.slot, start)
+            r += m
+        return {"row_segments": (off, (n, 4))}
+
+    def matrix_memory(self, qkvg, oq, ok, ov, og, z, bias_i, bias_f, cap, norm_w, eps, mult, out, ctx, cache, H, dk, dv):
+        """The mLSTM recurrence over the step's rows, request by request, from and into the state
+        slots; out [T, H*dv] = unit-RMS(per head) * norm_w * sigmoid(gate) * mult."""
+        self._dev(qkvg, z, bias_i, bias_f, norm_w, out, ctx.row_slot, cache.state)
+        T = qkvg.shape[0]
+        st = cache.state
+        per_slot = H * (dk * dv + dk + 1)
+        if z.dtype != torch.float32 or tuple(z.shape) != (T, 2 * H) or st.dtype != torch.float32 \
+                or st.shape[1] != per_slot or tuple(out.shape) != (T, H * dv) or out.dtype != qkvg.dtype \
+                or norm_w.numel() != H * dv or any(t.dtype != torch.float32 for t in (bias_i, bias_f, norm_w)):
+            raise BackendError("matrix_memory: bad operand types or shapes")
+        segs = ctx.aux.get("row_segments") if ctx.aux else None
+        fac = ctx.ws.get("mlstm_factors", (T, H * 4), torch.float32)
+        raw = ctx.ws.get("mlstm_raw", (T, H * dv), torch.float32)
+        code = self.lib("mlstm").zllm_mlstm(
+            _ptr(qkvg), c_int(qkvg.shape[1]), c_int(oq), c_int(ok), c_int(ov), c_int(og), _ptr(z), _ptr(bias_i), _ptr(bias_f),
+            c_float(cap), _ptr(norm_w), c_float(eps), c_float(mult), _ptr(segs), c_int(segs.shape[0] if segs is not None else 0),
+            _ptr(ctx.row_slot), _ptr(st), c_longlong(per_slot), _ptr(fac), _ptr(raw), _ptr(out), c_int(T), c_int(H),
+            c_int(dk), c_int(dv), c_int(qkvg.dtype == torch.bfloat16), self._stream())
+        self._check(code, "mlstm")
+        self.launches += 2
+
+    # ---- mixture of experts ------------------------------------------------------
+    def moe_route(self, h, w_router, top, groups, keep, idx, weights):
+        """Per row: softmax router scores, the ``top`` experts among the ``keep`` best of ``groups``
+        groups, their normalised weights."""
+        self._dev(h, w_router, idx, weights)
+        T, H = h.shape
+        E = w_router.shape[0]
+        if w_router.shape[1] != H or w_router.dtype != h.dtype or idx.dtype != torch.int32 or weights.dtype != torch.float32 \
+                or tuple(idx.shape) != (T, top) or tuple(weights.shape) != (T, top):
+            raise BackendError("moe_route: bad operand types or shapes")
+        code = self.lib("moe").zllm_moe_route(_ptr(h), _ptr(w_router), _ptr(idx), _ptr(weights), c_int(T), c_int(H), c_int(E),
+                                              c_int(top), c_int(groups), c_int(keep), c_int(h.dtype == torch.bfloat16),
+                                              self._stream())
+        self._check(code, "moe_route")
+
+    def moe_experts(self, h, idx, weights, w_gate, w_up, w_down, residual, scale, ws):
+        """residual[t] += scale * sum_j weights[t, j] * expert_{idx[t, j]}(h[t]); an expert is
+        down(silu(gate x) * (up x)).  w_gate, w_up [E, F, H], w_down [E, H, F]."""
+        self._dev(h, idx, weights, w_gate, w_up, w_down, residual)
+        T, H = h.shape
+        top = idx.shape[1]
+        E, F, _ = w_gate.shape
+        if tuple(w_gate.shape) != (E, F, H) or tuple(w_up.shape) != (E, F, H) or tuple(w_down.shape) != (E, H, F) \
+                or residual.dtype != torch.float32 or tuple(residual.shape) != (T, H) \
+                or any(t.dtype != h.dtype for t in (w_gate, w_up, w_down)):
+            raise BackendError("moe_experts: bad operand types or shapes")
+        n = T * top
+        off = ws.get("moe_offsets", (1, E + 1), torch.int32, cap=1)
+        perm = ws.get("moe_perm", (T, top), torch.int32)
+        act = ws.get("moe_act", (n, F), h.dtype, cap=ws.max_rows * top)
+        y = ws.get("moe_out", (n, H), torch.float32, cap=ws.max_rows * top)
+        moe, grouped = self.lib("moe"), self.lib("gemm_grouped")
+        is_bf16 = c_int(h.dtype == torch.bfloat16)
+        self._check(moe.zllm_moe_sort(_ptr(idx), _ptr(off), _ptr(perm), c_int(n), c_int(E), self._stream()), "moe_sort")
+        self._check(grouped.zllm_gemm_experts(_ptr(h), _ptr(w_gate), _ptr(w_up), _ptr(act), _ptr(off), _ptr(perm), c_int(top),
+                                              c_int(n), c_int(E), c_int(F), c_int(H), c_int(1), is_bf16, self._stream()),
+                    "gemm_experts")
+        self._check(grouped.zllm_gemm_experts(_ptr(act), _ptr(w_down), _ptr(None), _ptr(y), _ptr(off), _ptr(perm), c_int(top),
+                                              c_int(n), c_int(E), c_int(H), c_int(F), c_int(0), is_bf16, self._stream()),
+                    "gemm_experts")
+        self._check(moe.zllm_moe_combine(_ptr(y), _ptr(weights), _ptr(residual), c_int(T), c_int(H), c_int(top),
+                                         c_float(scale), self._stream()), "moe_combine")
 
     # ---- silu * up -----------------------------------------------------
     def silu_mul(self, a, b, out):

@@ -46,8 +46,9 @@ def _build_layers(spec: ModelSpec):
     for ls in spec.layers:
         if ls.arrangement not in _REGISTRIES["arrangement"]:
             raise ConfigError(f"unknown arrangement {ls.arrangement!r}")
-        layers.append(Layer(build("norm", ls.norm1), build("mixer", ls.mixer), build("norm", ls.norm2),
-                            build("feed_forward", ls.ffn), _REGISTRIES["arrangement"][ls.arrangement]))
+        has_ffn = ls.ffn is not None
+        layers.append(Layer(build("norm", ls.norm1), build("mixer", ls.mixer), build("norm", ls.norm2) if has_ffn else None,
+                            build("feed_forward", ls.ffn) if has_ffn else None, _REGISTRIES["arrangement"][ls.arrangement]))
     final_norm = build("norm", spec.final_norm)
     position = build("position_encoding", spec.embedding_position) if spec.embedding_position is not None else None
     return layers, final_norm, position
@@ -189,7 +190,7 @@ class DecoderModel:
         ops, rt = self.rt.ops, self.rt
         T = ctx.T
         x = ctx.ws.get("residual", (T, self.spec.hidden_size), torch.float32)
-        ops.embedding(ctx.token_ids, self.embedding, x)
+        ops.embedding(ctx.token_ids, self.embedding, x, self.spec.embedding_scale)
         if self.position is not None:
             self.position.on_embedding(x, ctx)
         for i, e in enumerate(self.spec.run_order):
@@ -209,4 +210,6 @@ class DecoderModel:
             hn = ctx.ws.get("head_in", (R, self.spec.hidden_size), rt.dtype, cap=R)
             self.final_norm.forward(rows, hn, ctx)
             ops.linear(hn, self.head, logits, "store")
+        if self.spec.logit_softcap:
+            ops.softcap(logits, self.spec.logit_softcap)
         return logits

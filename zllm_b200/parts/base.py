@@ -47,7 +47,7 @@ class WeightSpec:
     serving, float32 in the 32-bit path); "vector" keeps the stored dtype
     (a tensor stored in 32-bit stays so) and is only widened in the 32-bit path;
     "int" tables become int32.
-    init: ("normal", std) or ("one_plus_normal", std) for the random-weights mode.
+    init: ("normal", std), ("one_plus_normal", std) or ("constant", value) for the random-weights mode.
     """
 
     shape: Tuple[int, ...]
@@ -72,9 +72,9 @@ class LayerSpec:
     """
 
     mixer: PartSpec
-    ffn: PartSpec
+    ffn: Optional[PartSpec]             # None: the layer has no feed-forward (and then no norm2)
     norm1: PartSpec
-    norm2: PartSpec
+    norm2: Optional[PartSpec]
     arrangement: str = "pre_norm"
     tensor_names: Dict[str, str] = field(default_factory=dict)
 
@@ -96,7 +96,7 @@ class ModelSpec:
     architecture: str
     vocab_size: int
     hidden_size: int
-    max_position: int
+    max_position: Optional[int]         # None: the model sets no largest position (the engine's limit holds)
     layers: List[LayerSpec]
     run_order: List[RunEntry]
     final_norm: PartSpec
@@ -119,6 +119,10 @@ class ModelSpec:
     ignored_tensors: Tuple[str, ...] = ()
     # token ids that end a generation unless the caller says otherwise (a model's end-of-text ids)
     stop_token_ids: Tuple[int, ...] = ()
+    # the embedding rows are multiplied by this on their way into the residual stream
+    embedding_scale: float = 1.0
+    # logits <- cap * tanh(logits / cap) when set
+    logit_softcap: Optional[float] = None
 
 
 # --------------------------------------------------------------------------
@@ -128,11 +132,14 @@ class ModelSpec:
 
 @dataclass(frozen=True)
 class KVCacheSpec:
-    """Keys and values of every position (window None) or of the last ``window``."""
+    """Keys and values of every position (window None) or of the last ``window``.
+    ``values`` False: one row per position and head instead of a key row and a value row (a
+    mixer whose values are a part of what it caches as keys, e.g. a shared latent)."""
 
     n_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    values: bool = True
 
 
 @dataclass(frozen=True)

@@ -19,7 +19,12 @@ class Layer:
         self.arrangement = arrangement
 
     def parts(self):
-        return {"norm1": self.norm1, "mixer": self.mixer, "norm2": self.norm2, "ffn": self.ffn}
+        """The layer's parts by role; a layer without a feed-forward has neither ``ffn`` nor ``norm2``."""
+        out = {"norm1": self.norm1, "mixer": self.mixer}
+        if self.ffn is not None:
+            out["norm2"] = self.norm2
+            out["ffn"] = self.ffn
+        return out
 
     def run(self, x, ctx, cache, write_cache=True):
         self.arrangement(self, x, ctx, cache, write_cache)
@@ -35,6 +40,8 @@ def pre_norm(layer: Layer, x, ctx, cache, write_cache):
         h = ctx.ws.get("normed", tuple(x.shape), rt.dtype)
         layer.norm1.forward(x, h, ctx)
         layer.mixer.forward(h, x, ctx, cache, write_cache)
+    if layer.ffn is None:
+        return
     pro2 = layer.norm2.as_prologue() if layer.ffn.accepts_input_norm else None
     if pro2 is not None:
         layer.ffn.forward(x, x, ctx, input_norm=pro2)

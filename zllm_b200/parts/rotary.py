@@ -104,3 +104,71 @@ class Rotary(PositionEncoding):
 
     def rotary(self):
         return self._tables
+
+
+def yarn_frequencies(dims: int, base: float, factor: float, original: int, fast: float, slow: float):
+    """(frequencies of the dims/2 pairs, magnitude) under YaRN scaling.
+
+    g_i = base^(-2i/dims).  d(t) = dims ln(original / (2 pi t)) / (2 ln base) is the pair index whose
+    wave makes t turns over ``original`` positions; lo = max(floor(d(fast)), 0), hi = min(ceil(d(slow)),
+    dims - 1); ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1); pair i gets
+    g_i / factor * ramp_i + g_i * (1 - ramp_i): fast pairs keep their frequency, slow pairs are
+    stretched by ``factor``, a linear blend in between.  cos and sin are multiplied by
+    0.1 ln(factor) + 1.  Computed in double precision and rounded once to float32."""
+    if dims <= 0 or dims % 2:
+        raise ConfigError(f"rotary: dims {dims} must be positive and even")
+    i = torch.arange(dims // 2, dtype=torch.float64)
+    g = torch.pow(torch.tensor(float(base), dtype=torch.float64), -2.0 * i / dims)
+
+    def d(t):
+        return dims * math.log(original / (2.0 * math.pi * t)) / (2.0 * math.log(base))
+    lo = max(math.floor(d(fast)), 0)
+    hi = min(math.ceil(d(slow)), dims - 1)
+    ramp = torch.clamp((i - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+    return (g / factor * ramp + g * (1.0 - ramp)).to(torch.float32), 0.1 * math.log(factor) + 1.0
+
+
+@dataclass
+class RotaryFrequencies:
+    freq: torch.Tensor        # [dims/2] float32, on device
+    magnitude: float          # multiplies cos and sin
+    dims: int
+
+    def as_tuple(self):
+        return (self.freq, self.magnitude, self.dims)
+
+
+@register_position_encoding("rotary_on_the_fly")
+class RotaryOnTheFly(PositionEncoding):
+    """Rotary encoding without tables: kernels get the pairs' frequencies and compute the angle
+    position * frequency in float32 themselves, so there is no largest position.  Half-split
+    pairing (entry i with entry i + dims/2).  ``scaling`` None, or the YaRN constants
+    {factor, original, fast, slow}."""
+
+    capturable = True
+
+    def __init__(self, dims: int, base: float, scaling: Optional[dict] = None):
+        self.dims = int(dims)
+        self.base = float(base)
+        self.scaling = dict(scaling) if scaling else None
+        if self.scaling:
+            for k in ("factor", "original", "fast", "slow"):
+                if k not in self.scaling:
+                    raise ConfigError(f"rotary scaling is missing key {k!r}")
+            self.freq, self.magnitude = yarn_frequencies(self.dims, self.base, float(self.scaling["factor"]),
+                                                         self.scaling["original"], float(self.scaling["fast"]),
+                                                         float(self.scaling["slow"]))
+        else:
+            if self.dims <= 0 or self.dims % 2:
+                raise ConfigError(f"rotary: dims {self.dims} must be positive and even")
+            i = torch.arange(self.dims // 2, dtype=torch.float64)
+            self.freq = torch.pow(torch.tensor(self.base, dtype=torch.float64), -2.0 * i / self.dims).to(torch.float32)
+            self.magnitude = 1.0
+        self._on_device = None
+
+    def bind(self, rt):
+        super().bind(rt)
+        self._on_device = RotaryFrequencies(self.freq.to(rt.device).contiguous(), float(self.magnitude), self.dims)
+
+    def frequencies(self) -> RotaryFrequencies:
+        return self._on_device

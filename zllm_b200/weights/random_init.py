@@ -29,6 +29,8 @@ def _tensor_seed(seed: int, name: str) -> int:
 def random_tensor(name: str, spec: WeightSpec, seed: int, dtype=torch.float32, device="cpu",
                   std: float | None = None, norm_std: float | None = None) -> torch.Tensor:
     kind, own_std = spec.init
+    if kind == "constant":                  # a learned scalar's starting value (own_std is the value)
+        return torch.full(spec.shape, float(own_std), dtype=torch.float32, device=device).to(dtype)
     if kind == "one_plus_normal":
         std = norm_std if norm_std is not None else own_std
     elif std is None:
