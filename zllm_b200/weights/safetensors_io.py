@@ -107,7 +107,7 @@ def write_safetensors(path, tensors: Dict[str, torch.Tensor], metadata: Dict[str
         f.write(struct.pack("<Q", len(hjson)))
         f.write(hjson)
         for t in blobs:
-            f.write(t.view(torch.uint8).numpy().tobytes() if t.numel() else b"")
+            f.write(t.reshape(-1).view(torch.uint8).numpy().tobytes() if t.numel() else b"")      # reshape: a scalar has no axis to view
 
 
 def open_model_files(model_dir) -> Dict[str, SafetensorsFile]:
