@@ -6,6 +6,7 @@ bfloat16) on one B200, with prefill throughput, roofline fractions and end-to-en
     python bench.py --config 8b          # Llama-3.1-8B shape: decode to context 8192, prefill 2,048
     python bench.py --config 3b-mixed    # Llama-3.2-3B shape: 32 requests, 512-token portions beside decoding
     python bench.py --config cpu-baseline  # the plain CPU implementation of the test-suite, timed (no GPU)
+    python bench.py --config sepirax     # Sepirax at layer sizes of a real model beside Llama layers of equal width
 
 One JSON line on stdout.  ``value``: decode tokens/s at batch 8 near context 4096, K decode
 steps timed on the device with CUDA events (the steps replay a captured graph back to back,
@@ -191,6 +192,87 @@ def profile_case(args):
     return 0
 
 
+# Sepirax at sizes that resemble a real model's layers (random weights): width 2048, attention through a
+# latent of 512 + 64 rotated entries with 16 heads of 128 + 64, a matrix memory of 4 heads 256 x 512,
+# 32 experts of 1024 of which 4 are chosen among the best 2 of 4 groups.  Four layers, as the Llama
+# model it is measured beside (the 1B layer sizes, the same width, vocabulary and number of layers).
+def _sepirax_shape(layers=4, vocab=32000):
+    rot = {"base": 10000.0, "dims": 64, "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}}
+    att = {"heads": 16, "dim": 128, "rot_dim": 64, "vdim": 128, "q_rank": 768, "kv_rank": 512, "scale": 192 ** -0.5, "rot": rot}
+    mem = {"heads": 4, "dim": 256, "vdim": 512, "gate_cap": 15.0}
+    moe = {"kind": "moe", "expert": {"ff": 1024}, "router": {"experts": 32, "top": 4, "groups": {"count": 4, "keep": 2}}}
+    kinds = [("latent_attention", att), ("mlstm", mem)]
+    return {"architecture": "Sepirax", "vocab": vocab, "width": 2048, "norm": {"eps": 1e-6}, "residual_mult": 0.7,
+            "embedding": {"scale": 8.0}, "logit_softcap": 30.0,
+            "layers": [{"type": kinds[i % 2][0], "mixer": kinds[i % 2][1], "mlp": moe} for i in range(layers)]}
+
+
+def sepirax_bench(args):
+    """Prefill and decode of Sepirax beside the Llama layers of equal width: milliseconds, tokens/s and the
+    device time per kind of operation (a second pass with per-operation timers, graphs off)."""
+    import torch
+    from zllm_b200 import EngineConfig, LlamaConfig, ModelRunner, StepEntry
+    from zllm_b200.config import SepiraxConfig
+    from zllm_b200.kernels.ops import CudaOps
+
+    L, V, B, ctx_len = args.layers or 4, 32000, args.batch, args.context
+    models = {"sepirax": SepiraxConfig.from_dict(_sepirax_shape(L, V)),
+              "llama": LlamaConfig.from_dict(dict(MODEL, num_hidden_layers=L, vocab_size=V, tie_word_embeddings=False))}
+    gen = torch.Generator().manual_seed(0)
+    rand = lambda n: torch.randint(0, V, (n,), generator=gen).tolist()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sizes = (512, 2048)
+    out = {"config": "sepirax", "layers": L, "batch": B, "context": ctx_len, "dtype": "bf16", "data": "synthetic", "models": {}}
+    for name, cfg in models.items():
+        res = {}
+        for profiled in (False, True):
+            os.environ["ZLLM_PROFILE"] = "1" if profiled else ""
+            runner = ModelRunner(config=cfg, seed=3, random_on_device=True, ops=CudaOps("cuda:0"), engine_config=EngineConfig(
+                dtype="bfloat16", block_size=BLOCK, num_blocks=(B + 1) * (-(-(ctx_len + 2048 + 64) // BLOCK)), max_num_seqs=B + 1,
+                max_num_batched_tokens=2048, max_model_len=ctx_len + 2048 + 64, cuda_graphs=not profiled))
+            for T in sizes:
+                toks, times = rand(T), []
+                for i in range(2 if profiled else 5):
+                    s = runner.admit()
+                    if profiled:
+                        runner.ops.take_profile()
+                    torch.cuda.synchronize(); a.record()
+                    runner.step([StepEntry(s, toks, (T - 1,))])
+                    b.record(); torch.cuda.synchronize()
+                    times.append(a.elapsed_time(b))
+                    runner.release(s)
+                if profiled:
+                    res[f"prefill_{T}_kernel_ms"] = runner.ops.take_profile()
+                else:
+                    res[f"prefill_{T}_ms"] = round(min(times), 4)
+                    res[f"prefill_{T}_tok_s"] = round(T / min(times) * 1e3, 1)
+            slots = [runner.admit() for _ in range(B)]
+            for s in slots:
+                runner.step([StepEntry(s, rand(ctx_len), ())])
+            steps = 3 if profiled else max(8, min(args.steps, 64))
+            times = []
+            for i in range(steps + 3):
+                if profiled:
+                    runner.ops.take_profile()
+                torch.cuda.synchronize(); a.record()
+                runner.decode_step(slots, rand(B), [0.0] * B, [0] * B)
+                b.record(); torch.cuda.synchronize()
+                if i >= 3:
+                    times.append(a.elapsed_time(b))
+            if profiled:
+                res["decode_kernel_ms"] = runner.ops.take_profile()
+            else:
+                res["decode_ms_per_step"] = round(min(times), 4)
+                res["decode_tok_s"] = round(B / min(times) * 1e3, 1)
+                res["weight_bytes"] = runner.weight_bytes()
+            del runner
+            torch.cuda.empty_cache()
+        out["models"][name] = res
+    os.environ["ZLLM_PROFILE"] = ""
+    print(json.dumps(out))
+    return 0
+
+
 def mixed_workload(args, K, W):
     """BASELINE.json's fourth configuration: Llama-3.2-3B layer sizes (28 layers), 32 requests with
     prompt lengths drawn uniformly from 128..2048 (seeded), a token budget of 512 per step (prompt
@@ -326,7 +408,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=32)
     ap.add_argument("--impl", default="ours", choices=("ours", "reference"))
     ap.add_argument("--batch", type=int, default=8)
-    ap.add_argument("--config", default="1b", choices=("1b", "8b", "3b-mixed", "cpu-baseline"),
+    ap.add_argument("--config", default="1b", choices=("1b", "8b", "3b-mixed", "cpu-baseline", "sepirax"),
                     help="which of the configurations the numbers are quoted on (default: the 1B headline)")
     ap.add_argument("--case", default=None, choices=("decode", "prefill"),
                     help="run only a small case for a profiler: a few decode steps without graphs, or one prefill")
@@ -358,6 +440,8 @@ def main():
         return profile_case(args)
     if args.config == "3b-mixed":
         return mixed_workload(args, K, W)
+    if args.config == "sepirax":
+        return sepirax_bench(args)
 
     pk, pk_src = peaks()
     big = args.config == "8b"

@@ -114,13 +114,15 @@ def test_router(ops, dtype, E, top, groups, keep):
             # a close call between two experts (the sums run in another order): their scores must be as good as equal
             only_a, only_b = sorted(set(a) - set(b)), sorted(set(b) - set(a))
             assert len(only_a) == len(only_b) == 1 and \
-                abs(float(scores[t, only_a[0]] - scores[t, only_b[0]])) < 1e-4 * float(scores[t].max()), (t, a, b)
+                abs(float(scores[t, only_a[0]] - scores[t, only_b[0]])) < 1e-4 * float(scores[t].max()), (t, a, b, scores[t].tolist())
             continue
         assert all(abs(a[k] - b[k]) < 1e-5 for k in a)
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("T,H,F,E,top", [(1, 64, 32, 8, 2), (70, 96, 40, 6, 3), (300, 64, 24, 5, 1)])
+# widths and expert sizes that are multiples of 32 reach the tensor-core kernel in bfloat16, the others the CUDA-core one
+@pytest.mark.parametrize("T,H,F,E,top", [(1, 64, 32, 8, 2), (70, 96, 40, 6, 3), (300, 64, 24, 5, 1), (300, 128, 160, 4, 2),
+                                          (9, 256, 96, 16, 4), (700, 96, 72, 3, 1)])
 def test_experts(ops, dtype, T, H, F, E, top):
     from zllm_b200.engine.batch import Workspace
     g = torch.Generator().manual_seed(T)
@@ -156,13 +158,16 @@ def test_products_per_head(ops, dtype):
 
 # ---- attention through the latent ---------------------------------------------------------------------
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("H,dn,dr,dims,rank,q_rank,bs", [(4, 16, 8, 8, 48, 40, 16), (3, 24, 16, 8, 72, 56, 8), (9, 8, 0, 0, 200, 32, 16)])
+# the last three reach the tensor-core kernel in bfloat16 (a latent of 64, 128 or 512 entries, a rotated part of 16 x n)
+@pytest.mark.parametrize("H,dn,dr,dims,rank,q_rank,bs", [(4, 16, 8, 8, 48, 40, 16), (3, 24, 16, 8, 72, 56, 8), (9, 8, 0, 0, 200, 32, 16),
+                                                         (5, 16, 16, 16, 64, 40, 8), (20, 32, 32, 16, 128, 64, 16),
+                                                         (16, 16, 64, 64, 512, 96, 16)])
 def test_latent_attention_kernels(ops, dtype, H, dn, dr, dims, rank, q_rank, bs):
     from zllm_b200.cache import CacheManager
     from zllm_b200.parts import KVCacheSpec
     from zllm_b200.parts.rotary import yarn_frequencies
     g = torch.Generator().manual_seed(H)
-    cm = CacheManager([(KVCacheSpec(1, rank + dr, None, values=False), None)], bs, 40, 3, 40 * bs, dtype, DEV)
+    cm = CacheManager([(KVCacheSpec(1, rank + dr, None, values=False), None)], bs, 80, 3, 80 * bs, dtype, DEV)
     view = cm.view(0)
     assert view.v_pages is None
     if dims:
@@ -175,9 +180,12 @@ def test_latent_attention_kernels(ops, dtype, H, dn, dr, dims, rank, q_rank, bs)
     ld = q_rank + rank + dr + 8
     s0, s1 = cm.admit(), cm.admit()
     ref = RefOps()
-    plan = [[(s0, 37)], [(s0, 1), (s1, 2)], [(s1, 60), (s0, 1)], [(s0, 1)], [(s0, 33), (s1, 1)]]
+    plan = [[(s0, 37)], [(s0, 1), (s1, 2)], [(s1, 60), (s0, 1)], [(s0, 1)], [(s0, 33), (s1, 1)], [(s0, 250)], [(s1, 1), (s0, 1)],
+            [(s0, 1)]]
     for entries in plan:
-        ctx = _ctx(cm, entries)
+        # steps of single tokens only are given as the engine gives decode steps (no host-side description):
+        # long contexts are then taken in splits
+        ctx = _ctx(cm, entries, as_decode=all(n == 1 for _, n in entries))
         T = ctx.T
         proj = torch.randn(T, ld, generator=g).to(dtype)
         cq = torch.zeros(T, q_rank, dtype=dtype, device=DEV)

@@ -1,0 +1,178 @@
+// The experts' products on tensor cores (bfloat16 operands, float32 accumulation).
+//
+// Same contract as the per-expert kernel of gemm_grouped.cu: rows are (token, choice) pairs sorted
+// by expert, expert e owns the sorted range off[e]..off[e+1]-1, sorted entry i stands for pair
+// perm[i].  A CTA takes a tile of 128 sorted rows of ONE expert and 128 weight rows:
+//   first product  (swiglu): 64 gate rows and the 64 up rows of the same outputs; the rows of x are
+//                  gathered (x[perm[i] / top]); act[i][n] = silu(gate) * up in bfloat16;
+//   second product:          128 rows of the down matrix; y[perm[i]][n] in float32 (scattered).
+// K runs in steps of 32 through a three-stage cp.async ring; fragments come from shared memory with
+// ldmatrix and go to mma.sync m16n8k16; eight warps as 4 x 2, each 32 rows x 64 columns.  Every
+// output is the sum over k in a fixed order that depends on K alone, so a row's result does not
+// depend on which other rows share its tile.  Needs K % 32 == 0 and 16-byte aligned operands;
+// other sizes go to the CUDA-core kernel.
+#include "attention_common.cuh"
+
+#define TM 128
+#define TN 128
+#define TK 32
+#define LDS 40            // bfloat16 per shared-memory row: 80 bytes, so that ldmatrix rows fall on distinct banks
+#define STAGES 3
+
+__device__ __forceinline__ void cp_async16(void* dst, const void* src) {
+    const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(d), "l"(src));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+template <bool SWIGLU>
+__global__ void __launch_bounds__(256) gemm_experts_mma_kernel(const bf16* x, const bf16* __restrict__ w,
+                                                               const bf16* __restrict__ wu, void* out, const int* off,
+                                                               const int* perm, int top, int E, int N, int K) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    bf16* As = reinterpret_cast<bf16*>(smem_raw);            // [STAGES][TM][LDS]
+    bf16* Bs = As + STAGES * TM * LDS;                       // [STAGES][TN][LDS]
+    __shared__ int s_e, s_row0;
+    pdl_trigger();
+    pdl_wait();
+    if (threadIdx.x == 0) {
+        int tile = blockIdx.y, e = 0;
+        for (; e < E; ++e) {
+            const int tiles = (off[e + 1] - off[e] + TM - 1) / TM;
+            if (tile < tiles) break;
+            tile -= tiles;
+        }
+        s_e = e;
+        s_row0 = e < E ? off[e] + tile * TM : 0;
+    }
+    __syncthreads();
+    const int e = s_e;
+    if (e >= E) return;
+    const int row0 = s_row0, row_end = off[e + 1];
+    const int n0 = blockIdx.x * (SWIGLU ? TN / 2 : TN);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int wm = warp >> 1, wn = warp & 1;
+
+    // what this thread copies per stage: two 16-byte pieces of A rows and two of B rows
+    const bf16* a_src[2];
+    const bf16* b_src[2];
+    int dst[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int c = tid + i * 256, r = c >> 2, kc = c & 3;
+        int ri = row0 + r;
+        if (ri >= row_end) ri = row0;                        // rows beyond the expert's range repeat a real one; never stored
+        const size_t src = SWIGLU ? (size_t)(perm[ri] / top) : (size_t)ri;
+        a_src[i] = x + src * K + kc * 8;
+        int n;
+        const bf16* base;
+        if (SWIGLU) { n = n0 + (r & 63); base = (r < 64 ? w : wu) + (size_t)e * N * K; }
+        else { n = n0 + r; base = w + (size_t)e * N * K; }
+        if (n >= N) n = N - 1;
+        b_src[i] = base + (size_t)n * K + kc * 8;
+        dst[i] = r * LDS + kc * 8;
+    }
+    auto load_stage = [&](int st, int kt) {
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            cp_async16(As + st * TM * LDS + dst[i], a_src[i] + (size_t)kt * TK);
+            cp_async16(Bs + st * TN * LDS + dst[i], b_src[i] + (size_t)kt * TK);
+        }
+    };
+    float acc[2][8][4];
+#pragma unroll
+    for (int a = 0; a < 2; ++a)
+#pragma unroll
+        for (int b = 0; b < 8; ++b)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) acc[a][b][c] = 0.f;
+
+    const int KT = K / TK;
+#pragma unroll
+    for (int s = 0; s < STAGES - 1; ++s) {
+        if (s < KT) load_stage(s, s);
+        cp_async_commit();
+    }
+    for (int kt = 0; kt < KT; ++kt) {
+        cp_async_wait<STAGES - 2>();
+        __syncthreads();
+        if (kt + STAGES - 1 < KT) load_stage((kt + STAGES - 1) % STAGES, kt + STAGES - 1);
+        cp_async_commit();
+        const bf16* Ast = As + (kt % STAGES) * TM * LDS;
+        const bf16* Bst = Bs + (kt % STAGES) * TN * LDS;
+#pragma unroll
+        for (int ks = 0; ks < TK / 16; ++ks) {
+            unsigned af[2][4];
+#pragma unroll
+            for (int mt = 0; mt < 2; ++mt)
+                ldmatrix_x4(af[mt], Ast + (wm * 32 + mt * 16 + (lane & 15)) * LDS + ks * 16 + (lane >> 4) * 8);
+#pragma unroll
+            for (int p = 0; p < 4; ++p) {
+                // 16 weight rows per ldmatrix: with SWIGLU the warp's first 32 are gate rows, the last 32 their up rows
+                const int brow = SWIGLU ? (p < 2 ? wn * 32 + p * 16 : 64 + wn * 32 + (p - 2) * 16) : wn * 64 + p * 16;
+                unsigned bfr[4];
+                ldmatrix_x4(bfr, Bst + (brow + (lane & 7) + (lane >> 4) * 8) * LDS + ks * 16 + ((lane >> 3) & 1) * 8);
+#pragma unroll
+                for (int mt = 0; mt < 2; ++mt) {
+                    mma16816(acc[mt][2 * p], af[mt], bfr[0], bfr[1]);
+                    mma16816(acc[mt][2 * p + 1], af[mt], bfr[2], bfr[3]);
+                }
+            }
+        }
+    }
+    cp_async_wait<0>();
+    // epilogue: thread holds rows lane/4 (+8) and columns 2*(lane%4), +1 of every 16x8 tile
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int r = row0 + wm * 32 + mt * 16 + (lane >> 2) + half * 8;
+            if (r >= row_end) continue;
+            if (SWIGLU) {
+                bf16* orow = reinterpret_cast<bf16*>(out) + (size_t)r * N;
+#pragma unroll
+                for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+                    for (int c = 0; c < 2; ++c) {
+                        const int n = n0 + wn * 32 + nt * 8 + 2 * (lane & 3) + c;
+                        if (n >= N) continue;
+                        const float g = acc[mt][nt][half * 2 + c], u = acc[mt][nt + 4][half * 2 + c];
+                        orow[n] = __float2bfloat16_rn(g / (1.f + expf(-g)) * u);
+                    }
+            } else {
+                float* orow = reinterpret_cast<float*>(out) + (size_t)perm[r] * N;
+#pragma unroll
+                for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+                    for (int c = 0; c < 2; ++c) {
+                        const int n = n0 + wn * 64 + nt * 8 + 2 * (lane & 3) + c;
+                        if (n < N) orow[n] = acc[mt][nt][half * 2 + c];
+                    }
+            }
+        }
+}
+
+// As zllm_gemm_experts (gemm_grouped.cu) for bfloat16: swiglu != 0: out = act [n_pairs, N] bfloat16
+// in sorted order from gathered rows of x; swiglu == 0: out = y [n_pairs, N] float32 scattered.
+ZLLM_API int zllm_gemm_experts_mma(const void* x, const void* w, const void* wu, void* out, const int* off, const int* perm,
+                                   int top, int n_pairs, int E, int N, int K, int swiglu, void* stream) {
+    if (n_pairs <= 0 || N <= 0) return 0;
+    if (K <= 0 || (K % TK) || E <= 0 || top <= 0 || (((uintptr_t)x | (uintptr_t)w | (uintptr_t)wu) & 15)) return ZLLM_ERR_UNSUPPORTED;
+    cudaStream_t s = (cudaStream_t)stream;
+    const size_t smem = (size_t)STAGES * (TM + TN) * LDS * sizeof(bf16);
+    static bool raised = false;
+    if (!raised) {
+        cudaError_t e1 = cudaFuncSetAttribute(gemm_experts_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e2 = cudaFuncSetAttribute(gemm_experts_mma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e1 != cudaSuccess || e2 != cudaSuccess) return (int)(e1 != cudaSuccess ? e1 : e2);
+        raised = true;
+    }
+    const int n_cols = swiglu ? TN / 2 : TN;
+    dim3 grid((N + n_cols - 1) / n_cols, (n_pairs + TM - 1) / TM + E);
+    if (swiglu)
+        return launch_pdl(gemm_experts_mma_kernel<true>, grid, dim3(256), smem, s, (const bf16*)x, (const bf16*)w, (const bf16*)wu,
+                          out, off, perm, top, E, N, K);
+    return launch_pdl(gemm_experts_mma_kernel<false>, grid, dim3(256), smem, s, (const bf16*)x, (const bf16*)w, (const bf16*)wu,
+                      out, off, perm, top, E, N, K);
+}

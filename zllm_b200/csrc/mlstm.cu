@@ -9,8 +9,10 @@
 //   out = S'^T q / (max(|n' . q|, exp(-m')) + 1e-6),   q already times dk^(-1/2)
 //
 // Three kernels per step of the engine:
-//   mlstm_gates:  one warp per (segment, head) walks the segment's tokens in order: gates, m,
-//                 n and n.q; leaves (keep, take, denominator) per (row, head) and the new n, m.
+//   mlstm_gates:  one block per (segment, head): eight tokens at a time are staged in shared memory
+//                 (q, k, and the two gates with their tanh and logsigmoid), then one warp walks
+//                 them in order: m, n and n.q; leaves (keep, take, denominator) per (row, head)
+//                 and the new n, m.
 //   mlstm_scan:   blocks per (segment, head, slice of dv): each thread owns part of one column
 //                 of S in registers and walks the tokens in order; q, k, v and the per-token
 //                 factors come through shared memory eight tokens at a time.
@@ -36,48 +38,78 @@ __device__ __forceinline__ bool segment_of(const int* segs, const int* row_slot,
     return rows > 0 && slot >= 0;
 }
 
+#define ML_GTHREADS 128   // threads of a gates block: all stage a chunk, the first warp walks it
+#define ML_MAXDK (32 * ML_NL)
+
 template <typename AT>
-__global__ void __launch_bounds__(32) mlstm_gates_kernel(
+__global__ void __launch_bounds__(ML_GTHREADS) mlstm_gates_kernel(
     const AT* qkv, int ld, int oq, int ok, const float* z, const float* __restrict__ bi, const float* __restrict__ bf,
     float cap, float qscale, const int* __restrict__ segs, const int* row_slot, float* state, size_t state_stride,
     float* fac, int H, int dk, int dv) {
+    // a chunk of tokens is staged at once (loads that do not wait for one another), then walked in order
+    __shared__ float qk[ML_CHUNK][2 * ML_MAXDK / 4];         // q (scaled) then k of a token; see the launcher for dk > 128
+    __shared__ float gate[ML_CHUNK][2];
+    extern __shared__ float qk_big[];                        // used instead of ``qk`` when 2*dk exceeds its row
     pdl_trigger();
     pdl_wait();
-    const int h = blockIdx.y, lane = threadIdx.x;
+    const int h = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     int row0, rows, slot;
     if (!segment_of(segs, row_slot, blockIdx.x, row0, rows, slot)) return;
+    const bool big = 2 * dk > 2 * ML_MAXDK / 4;
+    float* stage = big ? qk_big : &qk[0][0];
+    const int per = big ? 2 * dk : 2 * ML_MAXDK / 4;
     float* st = state + (size_t)slot * state_stride + (size_t)h * ((size_t)dk * dv + dk + 1);
     float* np = st + (size_t)dk * dv;
     float n[ML_NL];
+    float m = 0.f;
+    if (warp == 0) {
 #pragma unroll
-    for (int i = 0; i < ML_NL; ++i) { const int r = lane + 32 * i; n[i] = r < dk ? np[r] : 0.f; }
-    float m = np[dk];
+        for (int i = 0; i < ML_NL; ++i) { const int r = lane + 32 * i; n[i] = r < dk ? np[r] : 0.f; }
+        m = np[dk];
+    }
     const float b_i = bi[h], b_f = bf[h];
-    for (int t = row0; t < row0 + rows; ++t) {
-        const float zi = z[(size_t)t * 2 * H + h], zf = z[(size_t)t * 2 * H + H + h];
-        const float gi = cap * tanhf((zi + b_i) / cap);
-        const float a = cap * tanhf((zf + b_f) / cap);
-        const float gf = fminf(a, 0.f) - log1pf(expf(-fabsf(a)));
-        const float m_new = fmaxf(gf + m, gi);
-        const float keep = expf(gf + m - m_new), take = expf(gi - m_new);
-        const AT* qr = qkv + (size_t)t * ld + oq + (size_t)h * dk;
-        const AT* kr = qkv + (size_t)t * ld + ok + (size_t)h * dk;
-        float dot = 0.f;
+    for (int c0 = 0; c0 < rows; c0 += ML_CHUNK) {
+        const int nc = min(ML_CHUNK, rows - c0);
+        __syncthreads();
+        for (int i = threadIdx.x; i < nc * 2 * dk; i += ML_GTHREADS) {
+            const int j = i / (2 * dk), e = i - j * 2 * dk;
+            const size_t t = (size_t)(row0 + c0 + j);
+            stage[j * per + e] = e < dk ? to_f32(qkv[t * ld + oq + (size_t)h * dk + e]) * qscale
+                                        : to_f32(qkv[t * ld + ok + (size_t)h * dk + (e - dk)]);
+        }
+        if (threadIdx.x < nc) {
+            const size_t t = (size_t)(row0 + c0 + threadIdx.x);
+            const float zi = z[t * 2 * H + h], zf = z[t * 2 * H + H + h];
+            const float a = cap * tanhf((zf + b_f) / cap);
+            gate[threadIdx.x][0] = cap * tanhf((zi + b_i) / cap);
+            gate[threadIdx.x][1] = fminf(a, 0.f) - log1pf(expf(-fabsf(a)));
+        }
+        __syncthreads();
+        if (warp != 0) continue;
+        for (int j = 0; j < nc; ++j) {
+            const float gi = gate[j][0], gf = gate[j][1];
+            const float m_new = fmaxf(gf + m, gi);
+            const float keep = expf(gf + m - m_new), take = expf(gi - m_new);
+            const float* q = stage + j * per;
+            const float* k = q + dk;
+            float dot = 0.f;
 #pragma unroll
-        for (int i = 0; i < ML_NL; ++i) {
-            const int r = lane + 32 * i;
-            if (r < dk) {
-                n[i] = keep * n[i] + take * to_f32(kr[r]);
-                dot = fmaf(n[i], to_f32(qr[r]) * qscale, dot);
+            for (int i = 0; i < ML_NL; ++i) {
+                const int r = lane + 32 * i;
+                if (r < dk) {
+                    n[i] = keep * n[i] + take * k[r];
+                    dot = fmaf(n[i], q[r], dot);
+                }
+            }
+            dot = warp_sum(dot);
+            m = m_new;
+            if (lane == 0) {
+                float* f = fac + ((size_t)(row0 + c0 + j) * H + h) * 4;
+                f[0] = keep; f[1] = take; f[2] = fmaxf(fabsf(dot), expf(-m)) + 1e-6f;
             }
         }
-        dot = warp_sum(dot);
-        m = m_new;
-        if (lane == 0) {
-            float* f = fac + ((size_t)t * H + h) * 4;
-            f[0] = keep; f[1] = take; f[2] = fmaxf(fabsf(dot), expf(-m)) + 1e-6f;
-        }
     }
+    if (warp != 0) return;
 #pragma unroll
     for (int i = 0; i < ML_NL; ++i) { const int r = lane + 32 * i; if (r < dk) np[r] = n[i]; }
     if (lane == 0) np[dk] = m;
@@ -188,10 +220,12 @@ ZLLM_API int zllm_mlstm(const void* qkv, int ld, int oq, int ok, int ov, int og,
     const int vs = ML_COLT / kp;
     const size_t smem = (size_t)ML_CHUNK * (2 * dk + vs + 4) * sizeof(float);
     dim3 grid(ns, H, (dv + vs - 1) / vs);
+    // the gates kernel stages q and k of a chunk: in its static array up to dk = 128, else in dynamic shared memory
+    const size_t gsmem = 2 * dk > 2 * ML_MAXDK / 4 ? (size_t)ML_CHUNK * 2 * dk * sizeof(float) : 0;
     int code;
     if (ns > 0) {
         if (is_bf16) {
-            code = launch_pdl(mlstm_gates_kernel<bf16>, dim3(ns, H), dim3(32), 0, s, (const bf16*)qkv, ld, oq, ok, z, bi, bf, cap,
+            code = launch_pdl(mlstm_gates_kernel<bf16>, dim3(ns, H), dim3(ML_GTHREADS), gsmem, s, (const bf16*)qkv, ld, oq, ok, z, bi, bf, cap,
                               qscale, segs, row_slot, state, (size_t)state_stride, fac, H, dk, dv);
             if (code) return code;
             if (rpt <= 32)
@@ -201,7 +235,7 @@ ZLLM_API int zllm_mlstm(const void* qkv, int ld, int oq, int ok, int ov, int og,
                 code = launch_pdl(mlstm_scan_kernel<bf16, 64>, grid, dim3(ML_COLT), smem, s, (const bf16*)qkv, ld, oq, ok, ov, fac,
                                   qscale, segs, row_slot, state, (size_t)state_stride, raw, H, dk, dv, kp);
         } else {
-            code = launch_pdl(mlstm_gates_kernel<float>, dim3(ns, H), dim3(32), 0, s, (const float*)qkv, ld, oq, ok, z, bi, bf,
+            code = launch_pdl(mlstm_gates_kernel<float>, dim3(ns, H), dim3(ML_GTHREADS), gsmem, s, (const float*)qkv, ld, oq, ok, z, bi, bf,
                               cap, qscale, segs, row_slot, state, (size_t)state_stride, fac, H, dk, dv);
             if (code) return code;
             if (rpt <= 32)

@@ -265,6 +265,9 @@ class CudaOps:
     SAMPLE_SCRATCH_ROWS = 1024
     TC_SCRATCH_BYTES = 64 * 1024 * 1024
     DECODE_MAX_ROWS = 16
+    LATENT_MMA_RANKS = (64, 128, 256, 512)      # latent sizes the tensor-core latent attention is built for
+    LATENT_MAX_SPLITS = 32
+    EXPERT_MMA_K = 32                   # the experts' tensor-core product steps through K in pieces of 32
 
     def _gemm_decode(self, x, norm_w, eps, w, out, mode, M, N, K, rope=None):
         """The fused decode product (csrc/gemm_decode.cu).  rope: (ctx, rot, cache, nq, nkv, hd, store)."""
@@ -501,6 +504,25 @@ class CudaOps:
                 or out.dtype != q.dtype or q.shape[1] != n_heads * q_off:
             raise BackendError("latent_attention: bad operand types or shapes")
         self._check_latent_cache(cache, rank + rot, q.dtype, "latent_attention")
+        if q.dtype == torch.bfloat16 and rank in self.LATENT_MMA_RANKS and rot % 16 == 0:
+            # tensor cores: the heads are the rows of the tile.  A step of single tokens only (decoding) has
+            # few rows: their keys are divided into splits of a multiple of 256 that a second kernel merges
+            n_splits, split_keys = 1, 0
+            if ctx.n_decode == T:
+                need = ctx.fixed_splits or self.decode_splits(ctx.max_context)
+                n_splits = max(1, min(need, self.LATENT_MAX_SPLITS))
+                split_keys = self.decode_split_keys * -(-need // n_splits)
+            part_o = part_ml = None
+            if n_splits > 1:
+                part_o = ctx.ws.get("latent_part_o", (T, n_heads * self.LATENT_MAX_SPLITS * rank), torch.float32, cap=T)
+                part_ml = ctx.ws.get("latent_part_ml", (T, n_heads * self.LATENT_MAX_SPLITS * 2), torch.float32, cap=T)
+            code = self.lib("latent_attention_mma").zllm_latent_attention_mma(
+                _ptr(q_lat), _ptr(q), c_int(q.shape[1]), c_int(q_off), _ptr(out), _ptr(part_o), _ptr(part_ml), _ptr(ctx.positions),
+                _ptr(ctx.row_slot), _ptr(cache.k_pages), _ptr(cache.block_table), c_int(cache.block_table.shape[1]),
+                c_int(cache.block_size), c_int(T), c_int(n_heads), c_int(rank), c_int(rot), _ptr(freqs[0]), c_float(freqs[1]),
+                c_int(freqs[2]), c_float(scale), c_int(n_splits), c_int(split_keys), self._stream())
+            self._check(code, "latent_attention_mma")
+            return
         code = self.lib("latent_attention").zllm_latent_attention(
             _ptr(q_lat), _ptr(q), c_int(q.shape[1]), c_int(q_off), _ptr(out), _ptr(ctx.positions), _ptr(ctx.row_slot),
             _ptr(cache.k_pages), _ptr(cache.block_table), c_int(cache.block_table.shape[1]), c_int(cache.block_size), c_int(T),
@@ -604,15 +626,22 @@ class CudaOps:
         perm = ws.get("moe_perm", (T, top), torch.int32)
         act = ws.get("moe_act", (n, F), h.dtype, cap=ws.max_rows * top)
         y = ws.get("moe_out", (n, H), torch.float32, cap=ws.max_rows * top)
-        moe, grouped = self.lib("moe"), self.lib("gemm_grouped")
-        is_bf16 = c_int(h.dtype == torch.bfloat16)
+        moe = self.lib("moe")
+        is_bf16 = h.dtype == torch.bfloat16
         self._check(moe.zllm_moe_sort(_ptr(idx), _ptr(off), _ptr(perm), c_int(n), c_int(E), self._stream()), "moe_sort")
-        self._check(grouped.zllm_gemm_experts(_ptr(h), _ptr(w_gate), _ptr(w_up), _ptr(act), _ptr(off), _ptr(perm), c_int(top),
-                                              c_int(n), c_int(E), c_int(F), c_int(H), c_int(1), is_bf16, self._stream()),
-                    "gemm_experts")
-        self._check(grouped.zllm_gemm_experts(_ptr(act), _ptr(w_down), _ptr(None), _ptr(y), _ptr(off), _ptr(perm), c_int(top),
-                                              c_int(n), c_int(E), c_int(H), c_int(F), c_int(0), is_bf16, self._stream()),
-                    "gemm_experts")
+        # each product goes to the tensor-core kernel when its K allows (bfloat16, K a multiple of 32),
+        # else to the CUDA-core kernel: decided by the sizes alone
+        for x_in, w_a, w_b, dst, N, K, swiglu in ((h, w_gate, w_up, act, F, H, 1), (act, w_down, None, y, H, F, 0)):
+            if is_bf16 and K % self.EXPERT_MMA_K == 0 and (x_in.data_ptr() | w_a.data_ptr() | (w_b.data_ptr() if w_b is not None else 0)) & 15 == 0:
+                code = self.lib("gemm_grouped_mma").zllm_gemm_experts_mma(
+                    _ptr(x_in), _ptr(w_a), _ptr(w_b), _ptr(dst), _ptr(off), _ptr(perm), c_int(top), c_int(n), c_int(E), c_int(N),
+                    c_int(K), c_int(swiglu), self._stream())
+                self._check(code, "gemm_experts_mma")
+            else:
+                code = self.lib("gemm_grouped").zllm_gemm_experts(
+                    _ptr(x_in), _ptr(w_a), _ptr(w_b), _ptr(dst), _ptr(off), _ptr(perm), c_int(top), c_int(n), c_int(E), c_int(N),
+                    c_int(K), c_int(swiglu), c_int(is_bf16), self._stream())
+                self._check(code, "gemm_experts")
         self._check(moe.zllm_moe_combine(_ptr(y), _ptr(weights), _ptr(residual), c_int(T), c_int(H), c_int(top),
                                          c_float(scale), self._stream()), "moe_combine")
 

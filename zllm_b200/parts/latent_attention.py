@@ -74,7 +74,8 @@ class LatentAttention(Mixer):
             self.position_encoding.bind(rt)
         prepare = getattr(rt.ops, "prepare", None)
         if prepare is not None:
-            prepare(self.KERNELS)
+            mma = rt.dtype == torch.bfloat16 and self.kv_rank in getattr(rt.ops, "LATENT_MMA_RANKS", ()) and self.dr % 16 == 0
+            prepare(self.KERNELS + (("latent_attention_mma",) if mma else ()))
 
     def load(self, tensors):
         H = self.H

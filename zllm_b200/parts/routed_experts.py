@@ -50,7 +50,7 @@ class RoutedExperts(FeedForward):
         super().bind(rt)
         prepare = getattr(rt.ops, "prepare", None)
         if prepare is not None:
-            prepare(self.KERNELS)
+            prepare(self.KERNELS + (("gemm_grouped_mma",) if rt.dtype == torch.bfloat16 else ()))
 
     def load(self, tensors):
         self.w_router = tensors["router"].contiguous()
