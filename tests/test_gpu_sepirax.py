@@ -121,7 +121,7 @@ def test_router(ops, dtype, E, top, groups, keep):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 # widths and expert sizes that are multiples of 32 reach the tensor-core kernel in bfloat16, the others the CUDA-core one
-@pytest.mark.parametrize("T,H,F,E,top", [(1, 64, 32, 8, 2), (70, 96, 40, 6, 3), (300, 64, 24, 5, 1), (300, 128, 160, 4, 2),
+@pytest.mark.parametrize("T,H,F,E,top", [(1, 64, 32, 8, 2), (70, 96, 40, 6, 3), (300, 64, 24, 5, 1), (300, 128, 160, 4, 2), (40, 128, 192, 8, 2),
                                           (9, 256, 96, 16, 4), (700, 96, 72, 3, 1)])
 def test_experts(ops, dtype, T, H, F, E, top):
     from zllm_b200.engine.batch import Workspace

@@ -6,7 +6,7 @@
 //   first product  (swiglu): 64 gate rows and the 64 up rows of the same outputs; the rows of x are
 //                  gathered (x[perm[i] / top]); act[i][n] = silu(gate) * up in bfloat16;
 //   second product:          128 rows of the down matrix; y[perm[i]][n] in float32 (scattered).
-// K runs in steps of 32 through a three-stage cp.async ring; fragments come from shared memory with
+// K runs in pieces of 32 or 64 through a cp.async ring of three or four stages; fragments come from shared memory with
 // ldmatrix and go to mma.sync m16n8k16; eight warps as 4 x 2, each 32 rows x 64 columns.  Every
 // output is the sum over k in a fixed order that depends on K alone, so a row's result does not
 // depend on which other rows share its tile.  Needs K % 32 == 0 and 16-byte aligned operands;
@@ -15,9 +15,10 @@
 
 #define TM 128
 #define TN 128
-#define TK 32
-#define LDS 40            // bfloat16 per shared-memory row: 80 bytes, so that ldmatrix rows fall on distinct banks
-#define STAGES 3
+// K is walked in pieces of TK = 32 through 3 stages (61 KB of shared memory, three CTAs per SM: many rows,
+// bound by the tensor cores) or of TK = 64 through 4 stages (147 KB, one CTA per SM with 64 KB of weights
+// in flight: few rows, bound by the stream of weights).  A shared-memory row holds TK + 8 bfloat16, so that
+// the eight rows of an ldmatrix fall on distinct banks.
 
 __device__ __forceinline__ void cp_async16(void* dst, const void* src) {
     const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
@@ -26,10 +27,11 @@ __device__ __forceinline__ void cp_async16(void* dst, const void* src) {
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
 template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
 
-template <bool SWIGLU>
+template <bool SWIGLU, int TK, int STAGES>
 __global__ void __launch_bounds__(256) gemm_experts_mma_kernel(const bf16* x, const bf16* __restrict__ w,
                                                                const bf16* __restrict__ wu, void* out, const int* off,
                                                                const int* perm, int top, int E, int N, int K) {
+    constexpr int LDS = TK + 8, PIECES = TK / 8, PER_THREAD = TM * PIECES / 256;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* As = reinterpret_cast<bf16*>(smem_raw);            // [STAGES][TM][LDS]
     bf16* Bs = As + STAGES * TM * LDS;                       // [STAGES][TN][LDS]
@@ -54,13 +56,13 @@ __global__ void __launch_bounds__(256) gemm_experts_mma_kernel(const bf16* x, co
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int wm = warp >> 1, wn = warp & 1;
 
-    // what this thread copies per stage: two 16-byte pieces of A rows and two of B rows
-    const bf16* a_src[2];
-    const bf16* b_src[2];
-    int dst[2];
+    // what this thread copies per stage: PER_THREAD 16-byte pieces of A rows and as many of B rows
+    const bf16* a_src[PER_THREAD];
+    const bf16* b_src[PER_THREAD];
+    int dst[PER_THREAD];
 #pragma unroll
-    for (int i = 0; i < 2; ++i) {
-        const int c = tid + i * 256, r = c >> 2, kc = c & 3;
+    for (int i = 0; i < PER_THREAD; ++i) {
+        const int c = tid + i * 256, r = c / PIECES, kc = c % PIECES;
         int ri = row0 + r;
         if (ri >= row_end) ri = row0;                        // rows beyond the expert's range repeat a real one; never stored
         const size_t src = SWIGLU ? (size_t)(perm[ri] / top) : (size_t)ri;
@@ -75,7 +77,7 @@ __global__ void __launch_bounds__(256) gemm_experts_mma_kernel(const bf16* x, co
     }
     auto load_stage = [&](int st, int kt) {
 #pragma unroll
-        for (int i = 0; i < 2; ++i) {
+        for (int i = 0; i < PER_THREAD; ++i) {
             cp_async16(As + st * TM * LDS + dst[i], a_src[i] + (size_t)kt * TK);
             cp_async16(Bs + st * TN * LDS + dst[i], b_src[i] + (size_t)kt * TK);
         }
@@ -158,21 +160,27 @@ __global__ void __launch_bounds__(256) gemm_experts_mma_kernel(const bf16* x, co
 ZLLM_API int zllm_gemm_experts_mma(const void* x, const void* w, const void* wu, void* out, const int* off, const int* perm,
                                    int top, int n_pairs, int E, int N, int K, int swiglu, void* stream) {
     if (n_pairs <= 0 || N <= 0) return 0;
-    if (K <= 0 || (K % TK) || E <= 0 || top <= 0 || (((uintptr_t)x | (uintptr_t)w | (uintptr_t)wu) & 15)) return ZLLM_ERR_UNSUPPORTED;
+    if (K <= 0 || (K % 32) || E <= 0 || top <= 0 || (((uintptr_t)x | (uintptr_t)w | (uintptr_t)wu) & 15)) return ZLLM_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
-    const size_t smem = (size_t)STAGES * (TM + TN) * LDS * sizeof(bf16);
+    const bool few = n_pairs <= 256 && K % 64 == 0;          // few rows: the deeper ring of wider pieces
+    const size_t smem = few ? (size_t)4 * (TM + TN) * 72 * sizeof(bf16) : (size_t)3 * (TM + TN) * 40 * sizeof(bf16);
     static bool raised = false;
     if (!raised) {
-        cudaError_t e1 = cudaFuncSetAttribute(gemm_experts_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        cudaError_t e2 = cudaFuncSetAttribute(gemm_experts_mma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e1 != cudaSuccess || e2 != cudaSuccess) return (int)(e1 != cudaSuccess ? e1 : e2);
+        const int big = 4 * (TM + TN) * 72 * (int)sizeof(bf16), small = 3 * (TM + TN) * 40 * (int)sizeof(bf16);
+        cudaError_t e = cudaFuncSetAttribute(gemm_experts_mma_kernel<true, 32, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, small);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_experts_mma_kernel<false, 32, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, small);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_experts_mma_kernel<true, 64, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_experts_mma_kernel<false, 64, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
+        if (e != cudaSuccess) return (int)e;
         raised = true;
     }
     const int n_cols = swiglu ? TN / 2 : TN;
     dim3 grid((N + n_cols - 1) / n_cols, (n_pairs + TM - 1) / TM + E);
-    if (swiglu)
-        return launch_pdl(gemm_experts_mma_kernel<true>, grid, dim3(256), smem, s, (const bf16*)x, (const bf16*)w, (const bf16*)wu,
-                          out, off, perm, top, E, N, K);
-    return launch_pdl(gemm_experts_mma_kernel<false>, grid, dim3(256), smem, s, (const bf16*)x, (const bf16*)w, (const bf16*)wu,
-                      out, off, perm, top, E, N, K);
+#define GE_GO(SW, TKV, STV) return launch_pdl(gemm_experts_mma_kernel<SW, TKV, STV>, grid, dim3(256), smem, s, (const bf16*)x, \
+                                              (const bf16*)w, (const bf16*)wu, out, off, perm, top, E, N, K)
+    if (swiglu && few) GE_GO(true, 64, 4);
+    if (swiglu) GE_GO(true, 32, 3);
+    if (few) GE_GO(false, 64, 4);
+    GE_GO(false, 32, 3);
+#undef GE_GO
 }

@@ -13,9 +13,9 @@
 //                 (q, k, and the two gates with their tanh and logsigmoid), then one warp walks
 //                 them in order: m, n and n.q; leaves (keep, take, denominator) per (row, head)
 //                 and the new n, m.
-//   mlstm_scan:   blocks per (segment, head, slice of dv): each thread owns part of one column
-//                 of S in registers and walks the tokens in order; q, k, v and the per-token
-//                 factors come through shared memory eight tokens at a time.
+//   mlstm_scan:   blocks per (segment, head, slice of dv): a group of lanes owns one column of S
+//                 in registers (16 rows per thread) and walks the tokens in order; q, k, v and
+//                 the per-token factors come through shared memory eight tokens at a time.
 //   mlstm_finish: per row and head: out / rms(out), times the norm weight, the output gate
 //                 sigmoid(g) and a constant.
 // A segment is the run of a request's rows in the step, (first row, rows, slot, ...), from a
@@ -27,7 +27,7 @@
 
 #define ML_NL 16          // n entries per lane: dk <= 512
 #define ML_CHUNK 8        // tokens staged at a time by the scan
-#define ML_COLT 128       // threads of a scan block
+#define ML_COLT 128
 
 __device__ __forceinline__ bool segment_of(const int* segs, const int* row_slot, int s, int& row0, int& rows, int& slot) {
     if (segs != nullptr) {
@@ -41,23 +41,75 @@ __device__ __forceinline__ bool segment_of(const int* segs, const int* row_slot,
 #define ML_GTHREADS 128   // threads of a gates block: all stage a chunk, the first warp walks it
 #define ML_MAXDK (32 * ML_NL)
 
+// eight consecutive operand values as float32 (the address is 16-byte aligned for bfloat16, 32 for float32)
+__device__ __forceinline__ void load8(const bf16* p, float (&v)[8]) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(h[i]); v[2 * i] = f.x; v[2 * i + 1] = f.y; }
+}
+__device__ __forceinline__ void load8(const float* p, float (&v)[8]) {
+    const float4 a = reinterpret_cast<const float4*>(p)[0], b = reinterpret_cast<const float4*>(p)[1];
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+
+// Stage q (scaled) and k of tokens t0 .. t0+nc-1 of head h into dst[j * per + (0..dk-1 | dk..2dk-1)].
+// vec: pieces of eight values by 16-byte loads, several in flight per thread; else value by value.
+template <typename AT, int NTHR>
+__device__ __forceinline__ void stage_qk(float* dst, int per, const AT* qkv, int ld, int oq, int ok, int h, int dk,
+                                         size_t t0, int nc, float qscale, int vec) {
+    if (vec) {
+        const int pieces = 2 * dk / 8;                         // per token
+        for (int i0 = threadIdx.x; i0 < nc * pieces; i0 += NTHR * 4) {
+            float v[4][8];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int i = i0 + u * NTHR;
+                if (i < nc * pieces) {
+                    const int j = i / pieces, e = (i - j * pieces) * 8;
+                    const AT* src = qkv + (t0 + j) * ld + (e < dk ? oq + (size_t)h * dk + e : ok + (size_t)h * dk + (e - dk));
+                    load8(src, v[u]);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int i = i0 + u * NTHR;
+                if (i < nc * pieces) {
+                    const int j = i / pieces, e = (i - j * pieces) * 8;
+                    const float sc = e < dk ? qscale : 1.f;
+                    float* d = dst + j * per + e;
+#pragma unroll
+                    for (int x = 0; x < 8; ++x) d[x] = v[u][x] * sc;
+                }
+            }
+        }
+        return;
+    }
+    for (int i = threadIdx.x; i < nc * 2 * dk; i += NTHR) {
+        const int j = i / (2 * dk), e = i - j * 2 * dk;
+        dst[j * per + e] = e < dk ? to_f32(qkv[(t0 + j) * ld + oq + (size_t)h * dk + e]) * qscale
+                                  : to_f32(qkv[(t0 + j) * ld + ok + (size_t)h * dk + (e - dk)]);
+    }
+}
+
 template <typename AT>
 __global__ void __launch_bounds__(ML_GTHREADS) mlstm_gates_kernel(
     const AT* qkv, int ld, int oq, int ok, const float* z, const float* __restrict__ bi, const float* __restrict__ bf,
     float cap, float qscale, const int* __restrict__ segs, const int* row_slot, float* state, size_t state_stride,
-    float* fac, int H, int dk, int dv) {
-    // a chunk of tokens is staged at once (loads that do not wait for one another), then walked in order
-    __shared__ float qk[ML_CHUNK][2 * ML_MAXDK / 4];         // q (scaled) then k of a token; see the launcher for dk > 128
+    float* fac, int H, int dk, int dv, int vec) {
+    // A chunk of eight tokens at a time: all threads stage q, k and the two log gates; then the first warp
+    // walks the chunk: the running maximum by one lane (a chain of a few operations per token), the
+    // exponentials of the chunk by eight lanes at once, n and the partial n.q token by token, and the
+    // eight sums over the lanes together at the end, so that few long latencies follow one another.
+    extern __shared__ float qk_stage[];                      // [ML_CHUNK][2 * dk]
     __shared__ float gate[ML_CHUNK][2];
-    extern __shared__ float qk_big[];                        // used instead of ``qk`` when 2*dk exceeds its row
+    __shared__ float coef[ML_CHUNK][3];                      // keep, take, exp(-m) per token
     pdl_trigger();
     pdl_wait();
     const int h = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     int row0, rows, slot;
     if (!segment_of(segs, row_slot, blockIdx.x, row0, rows, slot)) return;
-    const bool big = 2 * dk > 2 * ML_MAXDK / 4;
-    float* stage = big ? qk_big : &qk[0][0];
-    const int per = big ? 2 * dk : 2 * ML_MAXDK / 4;
+    const int per = 2 * dk;
     float* st = state + (size_t)slot * state_stride + (size_t)h * ((size_t)dk * dv + dk + 1);
     float* np = st + (size_t)dk * dv;
     float n[ML_NL];
@@ -71,12 +123,7 @@ __global__ void __launch_bounds__(ML_GTHREADS) mlstm_gates_kernel(
     for (int c0 = 0; c0 < rows; c0 += ML_CHUNK) {
         const int nc = min(ML_CHUNK, rows - c0);
         __syncthreads();
-        for (int i = threadIdx.x; i < nc * 2 * dk; i += ML_GTHREADS) {
-            const int j = i / (2 * dk), e = i - j * 2 * dk;
-            const size_t t = (size_t)(row0 + c0 + j);
-            stage[j * per + e] = e < dk ? to_f32(qkv[t * ld + oq + (size_t)h * dk + e]) * qscale
-                                        : to_f32(qkv[t * ld + ok + (size_t)h * dk + (e - dk)]);
-        }
+        stage_qk<AT, ML_GTHREADS>(qk_stage, per, qkv, ld, oq, ok, h, dk, (size_t)(row0 + c0), nc, qscale, vec);
         if (threadIdx.x < nc) {
             const size_t t = (size_t)(row0 + c0 + threadIdx.x);
             const float zi = z[t * 2 * H + h], zf = z[t * 2 * H + H + h];
@@ -86,28 +133,48 @@ __global__ void __launch_bounds__(ML_GTHREADS) mlstm_gates_kernel(
         }
         __syncthreads();
         if (warp != 0) continue;
-        for (int j = 0; j < nc; ++j) {
-            const float gi = gate[j][0], gf = gate[j][1];
-            const float m_new = fmaxf(gf + m, gi);
-            const float keep = expf(gf + m - m_new), take = expf(gi - m_new);
-            const float* q = stage + j * per;
-            const float* k = q + dk;
-            float dot = 0.f;
+        // the running maximum of the chunk, token by token; every lane computes it (no exchange needed)
+        float m_at[ML_CHUNK + 1];
+        m_at[0] = m;
 #pragma unroll
-            for (int i = 0; i < ML_NL; ++i) {
-                const int r = lane + 32 * i;
-                if (r < dk) {
-                    n[i] = keep * n[i] + take * k[r];
-                    dot = fmaf(n[i], q[r], dot);
+        for (int j = 0; j < ML_CHUNK; ++j) m_at[j + 1] = j < nc ? fmaxf(gate[j][1] + m_at[j], gate[j][0]) : m_at[j];
+#pragma unroll
+        for (int j = 0; j < ML_CHUNK; ++j)
+            if (lane == j && j < nc) {
+                coef[j][0] = expf(gate[j][1] + m_at[j] - m_at[j + 1]);
+                coef[j][1] = expf(gate[j][0] - m_at[j + 1]);
+                coef[j][2] = expf(-m_at[j + 1]);
+            }
+        m = m_at[ML_CHUNK];
+        __syncwarp();
+        float dot[ML_CHUNK];
+#pragma unroll
+        for (int j = 0; j < ML_CHUNK; ++j) {
+            dot[j] = 0.f;
+            if (j < nc) {
+                const float keep = coef[j][0], take = coef[j][1];
+                const float* q = qk_stage + j * per;
+                const float* k = q + dk;
+#pragma unroll
+                for (int i = 0; i < ML_NL; ++i) {
+                    const int r = lane + 32 * i;
+                    if (r < dk) {
+                        n[i] = keep * n[i] + take * k[r];
+                        dot[j] = fmaf(n[i], q[r], dot[j]);
+                    }
                 }
             }
-            dot = warp_sum(dot);
-            m = m_new;
-            if (lane == 0) {
-                float* f = fac + ((size_t)(row0 + c0 + j) * H + h) * 4;
-                f[0] = keep; f[1] = take; f[2] = fmaxf(fabsf(dot), expf(-m)) + 1e-6f;
-            }
         }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+            for (int j = 0; j < ML_CHUNK; ++j) dot[j] += __shfl_xor_sync(0xffffffffu, dot[j], o);
+#pragma unroll
+        for (int j = 0; j < ML_CHUNK; ++j)
+            if (lane == j && j < nc) {
+                float* f = fac + ((size_t)(row0 + c0 + j) * H + h) * 4;
+                f[0] = coef[j][0]; f[1] = coef[j][1]; f[2] = fmaxf(fabsf(dot[j]), coef[j][2]) + 1e-6f;
+            }
     }
     if (warp != 0) return;
 #pragma unroll
@@ -115,10 +182,16 @@ __global__ void __launch_bounds__(ML_GTHREADS) mlstm_gates_kernel(
     if (lane == 0) np[dk] = m;
 }
 
-template <typename AT, int RPT>     // RPT: rows of S per thread
+#undef ML_COLT
+#define ML_COLT 256       // threads of a scan block
+#define ML_RPT 16         // rows of S per thread
+
+template <typename AT>
 __global__ void __launch_bounds__(ML_COLT) mlstm_scan_kernel(
     const AT* qkv, int ld, int oq, int ok, int ov, const float* fac, float qscale, const int* __restrict__ segs,
-    const int* row_slot, float* state, size_t state_stride, float* out, int H, int dk, int dv, int kp) {
+    const int* row_slot, float* state, size_t state_stride, float* out, int H, int dk, int dv, int kp, int vec) {
+    // kp lanes share a column of S (rows sub, sub + kp, ...: ML_RPT of them per thread), so that a step is
+    // short and an SM holds many warps; the lanes' partial sums are added with shuffles.
     extern __shared__ float sm[];
     pdl_trigger();
     pdl_wait();
@@ -126,52 +199,53 @@ __global__ void __launch_bounds__(ML_COLT) mlstm_scan_kernel(
     int row0, rows, slot;
     if (!segment_of(segs, row_slot, blockIdx.x, row0, rows, slot)) return;
     const int vs = ML_COLT / kp;                      // columns of this block
-    const int sub = threadIdx.x % kp;                 // which rows of the column: sub, sub + kp, ...
-    const int col = blockIdx.z * vs + threadIdx.x / kp;
+    const int sub = threadIdx.x % kp;
+    const int lcol = threadIdx.x / kp;
+    const int col = blockIdx.z * vs + lcol;
     const bool has = col < dv;
     float* S = state + (size_t)slot * state_stride + (size_t)h * ((size_t)dk * dv + dk + 1);
-    float s[RPT];
+    float s[ML_RPT];
 #pragma unroll
-    for (int i = 0; i < RPT; ++i) { const int r = sub + i * kp; s[i] = (has && r < dk) ? S[(size_t)r * dv + col] : 0.f; }
+    for (int i = 0; i < ML_RPT; ++i) { const int r = sub + i * kp; s[i] = (has && r < dk) ? S[(size_t)r * dv + col] : 0.f; }
     const int per = 2 * dk + vs + 4;                  // floats staged per token: q, k, v slice, factors
     for (int c0 = 0; c0 < rows; c0 += ML_CHUNK) {
         const int nc = min(ML_CHUNK, rows - c0);
         __syncthreads();
-        for (int i = threadIdx.x; i < nc * per; i += ML_COLT) {
-            const int j = i / per, e = i - j * per;
+        stage_qk<AT, ML_COLT>(sm, per, qkv, ld, oq, ok, h, dk, (size_t)(row0 + c0), nc, qscale, vec);
+        for (int i = threadIdx.x; i < nc * (vs + 4); i += ML_COLT) {
+            const int j = i / (vs + 4), e = i - j * (vs + 4);
             const size_t t = (size_t)(row0 + c0 + j);
             float v;
-            if (e < dk) v = to_f32(qkv[t * ld + oq + (size_t)h * dk + e]) * qscale;
-            else if (e < 2 * dk) v = to_f32(qkv[t * ld + ok + (size_t)h * dk + (e - dk)]);
-            else if (e < 2 * dk + vs) {
-                const int cc = blockIdx.z * vs + (e - 2 * dk);
+            if (e < vs) {
+                const int cc = blockIdx.z * vs + e;
                 v = cc < dv ? to_f32(qkv[t * ld + ov + (size_t)h * dv + cc]) : 0.f;
-            } else v = fac[(t * H + h) * 4 + (e - 2 * dk - vs)];
-            sm[i] = v;
+            } else v = fac[(t * H + h) * 4 + (e - vs)];
+            sm[j * per + 2 * dk + e] = v;
         }
         __syncthreads();
         for (int j = 0; j < nc; ++j) {
             const float* q = sm + j * per;
             const float* k = q + dk;
-            const float vv = q[2 * dk + threadIdx.x / kp];
+            const float vv = q[2 * dk + lcol];
             const float keep = q[2 * dk + vs], take = q[2 * dk + vs + 1], den = q[2 * dk + vs + 2];
             const float tv = take * vv;
-            float num = 0.f;
+            float part[4] = {0.f, 0.f, 0.f, 0.f};         // four chains instead of one of dependent additions
 #pragma unroll
-            for (int i = 0; i < RPT; ++i) {
+            for (int i = 0; i < ML_RPT; ++i) {
                 const int r = sub + i * kp;
                 if (r < dk) {
                     s[i] = fmaf(tv, k[r], keep * s[i]);
-                    num = fmaf(s[i], q[r], num);
+                    part[i & 3] = fmaf(s[i], q[r], part[i & 3]);
                 }
             }
+            float num = (part[0] + part[1]) + (part[2] + part[3]);
             for (int o = 1; o < kp; o <<= 1) num += __shfl_xor_sync(0xffffffffu, num, o);
             if (has && sub == 0) out[(size_t)(row0 + c0 + j) * H * dv + (size_t)h * dv + col] = num / den;
         }
     }
     if (has) {
 #pragma unroll
-        for (int i = 0; i < RPT; ++i) { const int r = sub + i * kp; if (r < dk) S[(size_t)r * dv + col] = s[i]; }
+        for (int i = 0; i < ML_RPT; ++i) { const int r = sub + i * kp; if (r < dk) S[(size_t)r * dv + col] = s[i]; }
     }
 }
 
@@ -215,35 +289,28 @@ ZLLM_API int zllm_mlstm(const void* qkv, int ld, int oq, int ok, int ov, int og,
     const int ns = segs != nullptr ? n_seg : T;
     const float qscale = 1.f / sqrtf((float)dk);
     int kp = 1;
-    while (kp * 64 < dk) kp *= 2;                     // rows per thread <= 64
-    const int rpt = (dk + kp - 1) / kp;
+    while (kp * ML_RPT < dk) kp *= 2;                 // lanes per column of S: ML_RPT rows per thread, at most 32 lanes
     const int vs = ML_COLT / kp;
     const size_t smem = (size_t)ML_CHUNK * (2 * dk + vs + 4) * sizeof(float);
+    const size_t gsmem = (size_t)ML_CHUNK * 2 * dk * sizeof(float);
     dim3 grid(ns, H, (dv + vs - 1) / vs);
-    // the gates kernel stages q and k of a chunk: in its static array up to dk = 128, else in dynamic shared memory
-    const size_t gsmem = 2 * dk > 2 * ML_MAXDK / 4 ? (size_t)ML_CHUNK * 2 * dk * sizeof(float) : 0;
+    // pieces of eight values by 16-byte loads when every run of q and k starts on such a boundary
+    const int el = is_bf16 ? 2 : 4;
+    const int vec = (dk % 8 == 0 && ld % 8 == 0 && oq % 8 == 0 && ok % 8 == 0 && ((uintptr_t)qkv % (8 * el)) == 0) ? 1 : 0;
     int code;
     if (ns > 0) {
         if (is_bf16) {
-            code = launch_pdl(mlstm_gates_kernel<bf16>, dim3(ns, H), dim3(ML_GTHREADS), gsmem, s, (const bf16*)qkv, ld, oq, ok, z, bi, bf, cap,
-                              qscale, segs, row_slot, state, (size_t)state_stride, fac, H, dk, dv);
+            code = launch_pdl(mlstm_gates_kernel<bf16>, dim3(ns, H), dim3(ML_GTHREADS), gsmem, s, (const bf16*)qkv, ld, oq, ok, z,
+                              bi, bf, cap, qscale, segs, row_slot, state, (size_t)state_stride, fac, H, dk, dv, vec);
             if (code) return code;
-            if (rpt <= 32)
-                code = launch_pdl(mlstm_scan_kernel<bf16, 32>, grid, dim3(ML_COLT), smem, s, (const bf16*)qkv, ld, oq, ok, ov, fac,
-                                  qscale, segs, row_slot, state, (size_t)state_stride, raw, H, dk, dv, kp);
-            else
-                code = launch_pdl(mlstm_scan_kernel<bf16, 64>, grid, dim3(ML_COLT), smem, s, (const bf16*)qkv, ld, oq, ok, ov, fac,
-                                  qscale, segs, row_slot, state, (size_t)state_stride, raw, H, dk, dv, kp);
+            code = launch_pdl(mlstm_scan_kernel<bf16>, grid, dim3(ML_COLT), smem, s, (const bf16*)qkv, ld, oq, ok, ov, fac,
+                              qscale, segs, row_slot, state, (size_t)state_stride, raw, H, dk, dv, kp, vec);
         } else {
-            code = launch_pdl(mlstm_gates_kernel<float>, dim3(ns, H), dim3(ML_GTHREADS), gsmem, s, (const float*)qkv, ld, oq, ok, z, bi, bf,
-                              cap, qscale, segs, row_slot, state, (size_t)state_stride, fac, H, dk, dv);
+            code = launch_pdl(mlstm_gates_kernel<float>, dim3(ns, H), dim3(ML_GTHREADS), gsmem, s, (const float*)qkv, ld, oq, ok,
+                              z, bi, bf, cap, qscale, segs, row_slot, state, (size_t)state_stride, fac, H, dk, dv, vec);
             if (code) return code;
-            if (rpt <= 32)
-                code = launch_pdl(mlstm_scan_kernel<float, 32>, grid, dim3(ML_COLT), smem, s, (const float*)qkv, ld, oq, ok, ov,
-                                  fac, qscale, segs, row_slot, state, (size_t)state_stride, raw, H, dk, dv, kp);
-            else
-                code = launch_pdl(mlstm_scan_kernel<float, 64>, grid, dim3(ML_COLT), smem, s, (const float*)qkv, ld, oq, ok, ov,
-                                  fac, qscale, segs, row_slot, state, (size_t)state_stride, raw, H, dk, dv, kp);
+            code = launch_pdl(mlstm_scan_kernel<float>, grid, dim3(ML_COLT), smem, s, (const float*)qkv, ld, oq, ok, ov, fac,
+                              qscale, segs, row_slot, state, (size_t)state_stride, raw, H, dk, dv, kp, vec);
         }
         if (code) return code;
     }
