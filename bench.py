@@ -221,11 +221,13 @@ def sepirax_bench(args):
     gen = torch.Generator().manual_seed(0)
     rand = lambda n: torch.randint(0, V, (n,), generator=gen).tolist()
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    sizes = (512, 2048)
+    sizes = (512, 2048) if args.tokens > 0 else ()          # --tokens 0: the decode part only (for a launch list)
     out = {"config": "sepirax", "layers": L, "batch": B, "context": ctx_len, "dtype": "bf16", "data": "synthetic", "models": {}}
+    if args.shape == "sepirax-only":
+        models.pop("llama")
     for name, cfg in models.items():
         res = {}
-        for profiled in (False, True):
+        for profiled in ((False,) if args.tokens == 0 else (False, True)):
             os.environ["ZLLM_PROFILE"] = "1" if profiled else ""
             runner = ModelRunner(config=cfg, seed=3, random_on_device=True, ops=CudaOps("cuda:0"), engine_config=EngineConfig(
                 dtype="bfloat16", block_size=BLOCK, num_blocks=(B + 1) * (-(-(ctx_len + 2048 + 64) // BLOCK)), max_num_seqs=B + 1,
@@ -417,7 +419,8 @@ def main():
     ap.add_argument("--layers", type=int, default=None, help="--case: fewer layers (profiling only)")
     ap.add_argument("--graphs", action="store_true", help="--case: with CUDA graphs (default off, so that a profiler sees "
                     "every kernel as its own launch)")
-    ap.add_argument("--shape", default="1b", choices=sorted(SHAPES), help="--case: layer sizes of another Llama shape")
+    ap.add_argument("--shape", default="1b", choices=sorted(SHAPES) + ["sepirax-only"],
+                    help="--case: layer sizes of another Llama shape; --config sepirax: sepirax-only leaves the Llama model out")
     args = ap.parse_args()
 
     if args.config == "cpu-baseline":

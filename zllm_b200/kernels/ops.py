@@ -109,30 +109,34 @@ class CudaOps:
         if dtype not in (torch.bfloat16, torch.float32):
             raise BackendError(f"unsupported activation dtype {dtype}")
         self.dtype = dtype
-        names = ["elementwise", "gemm_plain", "attention_plain", "sampling"]
+        # What every model needs is built (in parallel) and loaded now; a part's own kernels (attention of
+        # one kind or another, experts, a recurrence) when the part is bound (``prepare``) or, failing
+        # that, at their first use (``lib``): a program compiles what its model needs, and no more.
+        names = ["elementwise", "gemm_plain", "sampling"]
         if dtype == torch.bfloat16:
-            names += ["gemm_decode", "gemm_stream", "gemm_tc", "attention_bf16", "attention_decode_tma", "attention_prefill_tc"]
-        build.build(names)
-        for n in names:
-            self._libs[n] = build.load(n)
-        if dtype == torch.bfloat16 and os.environ.get("ZLLM_GEMM_PAIR", "") == "0":
-            # measurement switch: the many-row products on single CTAs (tiles of 128 rows) only
-            self._libs["gemm_tc"].zllm_gemm_tc_force_pair(0)
+            names += ["gemm_decode", "gemm_stream", "gemm_tc"]
         # a word of pinned host memory per kernel family with bounded waits: a wait that gives up
         # writes its code there too, so the engine sees it where it synchronises anyway, without a copy
         if self._error_words is None:
             self._error_words = torch.zeros(len(self.WAIT_FAMILIES), dtype=torch.int32).pin_memory()
-        for i, (name, prefix) in enumerate(self.WAIT_FAMILIES):
-            lib = self._libs.get(name)
-            if lib is not None:
-                code = getattr(lib, prefix + "_set_error_mirror")(c_void_p(self._error_words.data_ptr() + 4 * i))
-                if code != 0:
-                    raise BackendError(f"{name}: cannot set the error mirror (CUDA error {code})")
+        self.prepare(names)
+        if dtype == torch.bfloat16 and os.environ.get("ZLLM_GEMM_PAIR", "") == "0":
+            # measurement switch: the many-row products on single CTAs (tiles of 128 rows) only
+            self._libs["gemm_tc"].zllm_gemm_tc_force_pair(0)
+
+    # the attention kernels of the paged key/value cache, by activation dtype
+    PAGED_ATTENTION_KERNELS = {torch.float32: ("attention_plain",),
+                               torch.bfloat16: ("attention_plain", "attention_bf16", "attention_decode_tma", "attention_prefill_tc")}
 
     def lib(self, name):
         lib = self._libs.get(name)
         if lib is None:
             lib = self._libs[name] = build.load(name)
+            for i, (family, prefix) in enumerate(self.WAIT_FAMILIES):
+                if family == name and self._error_words is not None:
+                    code = getattr(lib, prefix + "_set_error_mirror")(c_void_p(self._error_words.data_ptr() + 4 * i))
+                    if code != 0:
+                        raise BackendError(f"{name}: cannot set the error mirror (CUDA error {code})")
         return lib
 
     def prepare(self, names):
@@ -142,7 +146,7 @@ class CudaOps:
         if names:
             build.build(names)
             for n in names:
-                self._libs[n] = build.load(n)
+                self.lib(n)
 
     def _stream(self):
         if self._bound_stream is not None:
@@ -221,7 +225,7 @@ class CudaOps:
             raise BackendError(f"linear: shapes x{tuple(x.shape)} w{tuple(w.shape)} out{tuple(out.shape)} mode {mode}")
         if mode == "add" and out.dtype != torch.float32:
             raise BackendError("linear: the 'add' epilogue accumulates into float32")
-        if x.dtype == torch.bfloat16 and "gemm_decode" in self._libs and self._linear_bf16(x, w, out, mode, M, N, K):
+        if x.dtype == torch.bfloat16 and self.dtype == torch.bfloat16 and self._linear_bf16(x, w, out, mode, M, N, K):
             return
         code = self.lib("gemm_plain").zllm_gemm_plain(_ptr(x), _ptr(w), _ptr(out), c_int(M), c_int(N), c_int(K),
                                                       c_int(MODES[mode]), c_int(x.dtype == torch.bfloat16),
@@ -362,7 +366,7 @@ class CudaOps:
             x = h
         # many rows: rotation and cache write in the epilogue of the tensor-core product (head sizes
         # 64 and 128, half-split pairs over the whole head); otherwise a pass of their own over qkv
-        if M >= self.ROPE_IN_PRODUCT_MIN_ROWS and "gemm_tc" in self._libs and x.dtype == torch.bfloat16 and qkv.dtype == torch.bfloat16 \
+        if M >= self.ROPE_IN_PRODUCT_MIN_ROWS and self.dtype == torch.bfloat16 and x.dtype == torch.bfloat16 and qkv.dtype == torch.bfloat16 \
                 and w_qkv.dtype == torch.bfloat16 and hd in (64, 128) and K % 8 == 0 \
                 and (rot is None or (rot.rot_dim == hd and not rot.interleaved)) \
                 and (x.data_ptr() | w_qkv.data_ptr() | qkv.data_ptr()) & 15 == 0:
@@ -399,7 +403,7 @@ class CudaOps:
         if M <= self.DECODE_MAX_ROWS:
             self._gemm_decode(x, None, 0.0, w, out, mode, M, N, K)
             return True
-        if tc_ok and "gemm_tc" in self._libs:
+        if tc_ok:
             if self._tc_scratch is None:     # float32 partial tiles of products whose K is split (few tiles)
                 self._tc_scratch = torch.empty(self.TC_SCRATCH_BYTES // 4, dtype=torch.float32, device=self.device)
             code = self.lib("gemm_tc").zllm_gemm_tc_bf16(_ptr(x), _ptr(w), _ptr(out), c_int(M), c_int(N), c_int(K),
@@ -704,7 +708,7 @@ class CudaOps:
         self._check_cache(cache, nkv, hd, qkv.dtype, "paged_attention")
         if tuple(out.shape) != (T, nq * hd) or out.dtype != qkv.dtype:
             raise BackendError("paged_attention: output does not match")
-        if qkv.dtype == torch.bfloat16 and "attention_bf16" in self._libs and \
+        if qkv.dtype == torch.bfloat16 and self.dtype == torch.bfloat16 and \
                 self._attention_bf16(qkv, out, ctx, cache, nq, nkv, hd, scale, window):
             return
         self.attention_plain(qkv, out, ctx.positions, ctx.row_slot, cache, nq, nkv, hd, scale, window)

@@ -62,6 +62,9 @@ class PagedAttention(Mixer):
         super().bind(rt)
         if self.position_encoding is not None and self.position_encoding.rt is None:
             self.position_encoding.bind(rt)
+        prepare = getattr(rt.ops, "prepare", None)
+        if prepare is not None:                     # the attention kernels of this precision, built together
+            prepare(rt.ops.PAGED_ATTENTION_KERNELS[rt.dtype])
 
     def load(self, tensors):
         self.w_qkv = torch.cat([tensors["q_proj"], tensors["k_proj"], tensors["v_proj"]], dim=0).contiguous()
