@@ -16,7 +16,7 @@
 #define TM 128
 #define TN 128
 // K is walked in pieces of TK = 32 through 3 stages (61 KB of shared memory, three CTAs per SM: many rows,
-// bound by the tensor cores) or of TK = 64 through 4 stages (147 KB, one CTA per SM with 64 KB of weights
+// bound by the tensor cores) or of TK = 64 through 3 stages (110 KB, two CTAs per SM with 72 KB of weights
 // in flight: few rows, bound by the stream of weights).  A shared-memory row holds TK + 8 bfloat16, so that
 // the eight rows of an ldmatrix fall on distinct banks.
 
@@ -38,15 +38,32 @@ __global__ void __launch_bounds__(256) gemm_experts_mma_kernel(const bf16* x, co
     __shared__ int s_e, s_row0;
     pdl_trigger();
     pdl_wait();
-    if (threadIdx.x == 0) {
-        int tile = blockIdx.y, e = 0;
-        for (; e < E; ++e) {
-            const int tiles = (off[e + 1] - off[e] + TM - 1) / TM;
-            if (tile < tiles) break;
-            tile -= tiles;
+    if (threadIdx.x < 32) {
+        // which (expert, tile of its rows) is tile blockIdx.y: the experts' tile counts 32 at a time, a prefix
+        // sum over the lanes, the first expert whose running total passes the tile
+        const int lane_ = threadIdx.x;
+        int before = 0, found_e = E, found_row0 = 0;
+        for (int e0 = 0; e0 < E && found_e == E; e0 += 32) {
+            const int ee = e0 + lane_;
+            const int lo = ee < E ? off[ee] : 0;
+            const int tiles = ee < E ? (off[ee + 1] - lo + TM - 1) / TM : 0;
+            int incl = tiles;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int v = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane_ >= o) incl += v;
+            }
+            const int start = before + incl - tiles;                      // tiles before this lane's expert
+            const bool mine = tiles > 0 && (int)blockIdx.y >= start && (int)blockIdx.y < start + tiles;
+            const unsigned who = __ballot_sync(0xffffffffu, mine);
+            if (who) {
+                const int src = __ffs(who) - 1;
+                found_e = e0 + src;
+                found_row0 = __shfl_sync(0xffffffffu, lo + ((int)blockIdx.y - start) * TM, src);
+            }
+            before += __shfl_sync(0xffffffffu, incl, 31);
         }
-        s_e = e;
-        s_row0 = e < E ? off[e] + tile * TM : 0;
+        if (lane_ == 0) { s_e = found_e; s_row0 = found_row0; }
     }
     __syncthreads();
     const int e = s_e;
@@ -163,14 +180,14 @@ ZLLM_API int zllm_gemm_experts_mma(const void* x, const void* w, const void* wu,
     if (K <= 0 || (K % 32) || E <= 0 || top <= 0 || (((uintptr_t)x | (uintptr_t)w | (uintptr_t)wu) & 15)) return ZLLM_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
     const bool few = n_pairs <= 256 && K % 64 == 0;          // few rows: the deeper ring of wider pieces
-    const size_t smem = few ? (size_t)4 * (TM + TN) * 72 * sizeof(bf16) : (size_t)3 * (TM + TN) * 40 * sizeof(bf16);
+    const size_t smem = few ? (size_t)3 * (TM + TN) * 72 * sizeof(bf16) : (size_t)3 * (TM + TN) * 40 * sizeof(bf16);
     static bool raised = false;
     if (!raised) {
-        const int big = 4 * (TM + TN) * 72 * (int)sizeof(bf16), small = 3 * (TM + TN) * 40 * (int)sizeof(bf16);
+        const int big = 3 * (TM + TN) * 72 * (int)sizeof(bf16), small = 3 * (TM + TN) * 40 * (int)sizeof(bf16);
         cudaError_t e = cudaFuncSetAttribute(gemm_experts_mma_kernel<true, 32, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, small);
         if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_experts_mma_kernel<false, 32, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, small);
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_experts_mma_kernel<true, 64, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_experts_mma_kernel<false, 64, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_experts_mma_kernel<true, 64, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_experts_mma_kernel<false, 64, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
         if (e != cudaSuccess) return (int)e;
         raised = true;
     }
@@ -178,9 +195,9 @@ ZLLM_API int zllm_gemm_experts_mma(const void* x, const void* w, const void* wu,
     dim3 grid((N + n_cols - 1) / n_cols, (n_pairs + TM - 1) / TM + E);
 #define GE_GO(SW, TKV, STV) return launch_pdl(gemm_experts_mma_kernel<SW, TKV, STV>, grid, dim3(256), smem, s, (const bf16*)x, \
                                               (const bf16*)w, (const bf16*)wu, out, off, perm, top, E, N, K)
-    if (swiglu && few) GE_GO(true, 64, 4);
+    if (swiglu && few) GE_GO(true, 64, 3);
     if (swiglu) GE_GO(true, 32, 3);
-    if (few) GE_GO(false, 64, 4);
+    if (few) GE_GO(false, 64, 3);
     GE_GO(false, 32, 3);
 #undef GE_GO
 }

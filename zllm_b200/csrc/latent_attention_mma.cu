@@ -12,13 +12,14 @@
 //               warp), keeps the running maximum and sum of its rows, and packs P as its A operand;
 //   O += P V:   warp w owns RANK / 4 columns of the latent; V is the key tile itself, read with
 //               ldmatrix.trans.
-// With few rows in a step (decoding) the keys of a row are divided into splits of 256 over
+// With few rows in a step (decoding) the keys of a row are divided into splits (whole key blocks) over
 // gridDim.z; the partial (maximum, sum, O) of the splits are merged by a second kernel.
 // Sizes: RANK in {64, 128, 256, 512}, rot a multiple of 16; others go to the CUDA-core kernel.
 #include "attention_common.cuh"
 
 #define LM_KEYS 32
 #define LM_HEADS 16
+#define LM_MAXHALF 128          // rotated pairs per head at most
 
 __device__ __forceinline__ void lm_cp_async16(void* dst, const void* src) {
     const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
@@ -55,8 +56,16 @@ __global__ void __launch_bounds__(128) latent_attention_mma_kernel(
     const int k_begin = split * split_keys;
     const int k_end = slot < 0 ? 0 : min(pos + 1, n_splits > 1 ? k_begin + split_keys : pos + 1);
     if (k_begin < k_end) {
-        // ---- the queries of the 16 heads: latent side as given, rotated side rotated here
+        // ---- the queries of the 16 heads: latent side as given, rotated side rotated here (the row's
+        //      cosines and sines once, for all heads)
+        __shared__ float rc[LM_MAXHALF], rs[LM_MAXHALF];
         const int half = dims >> 1;
+        for (int j = tid; j < half; j += 128) {
+            const float ang = __fmul_rn((float)pos, freq[j]);
+            rc[j] = cosf(ang) * mag;
+            rs[j] = sinf(ang) * mag;
+        }
+        __syncthreads();
         for (int i = tid; i < LM_HEADS * D; i += 128) {
             const int row = i / D, d = i - row * D;
             const int h = g * LM_HEADS + row;
@@ -68,10 +77,8 @@ __global__ void __launch_bounds__(128) latent_attention_mma_kernel(
                     const int e = d - RANK;
                     if (e < dims) {
                         const int j = e < half ? e : e - half;
-                        const float ang = __fmul_rn((float)pos, freq[j]);
-                        const float c = cosf(ang) * mag, s = sinf(ang) * mag;
                         const float a = to_f32(qr[j]), b = to_f32(qr[j + half]);
-                        v = e < half ? a * c - b * s : b * c + a * s;
+                        v = e < half ? a * rc[j] - b * rs[j] : b * rc[j] + a * rs[j];
                     } else v = to_f32(qr[e]);
                 }
             }
@@ -79,15 +86,18 @@ __global__ void __launch_bounds__(128) latent_attention_mma_kernel(
         }
         const int* trow = table + (size_t)slot * max_blocks;
         const int chunks = D / 8;                                      // 16-byte pieces of a cache row
+        // a warp brings in every fourth key of the block: one page lookup per key, the lanes over its pieces
         auto load_block = [&](int st, int base) {
             bf16* dst = Ks + st * LM_KEYS * LDK;
-            for (int i = tid; i < LM_KEYS * chunks; i += 128) {
-                const int j = i / chunks, c = i - j * chunks;
+            for (int j = warp; j < LM_KEYS; j += 4) {
                 const int key = base + j;
                 int page = -1;
                 if (key < k_end) page = trow[key / bs];
-                if (page >= 0) lm_cp_async16(dst + j * LDK + c * 8, pages + ((size_t)page * bs + (key % bs)) * D + c * 8);
-                else *reinterpret_cast<uint4*>(dst + j * LDK + c * 8) = make_uint4(0u, 0u, 0u, 0u);   // no key: zeros, never garbage
+                const bf16* src = pages + ((size_t)(page >= 0 ? page : 0) * bs + (key % bs)) * D;
+                for (int c = lane; c < chunks; c += 32) {
+                    if (page >= 0) lm_cp_async16(dst + j * LDK + c * 8, src + c * 8);
+                    else *reinterpret_cast<uint4*>(dst + j * LDK + c * 8) = make_uint4(0u, 0u, 0u, 0u);   // no key: zeros, never garbage
+                }
             }
         };
         const int n_blocks = (k_end - k_begin + LM_KEYS - 1) / LM_KEYS;
@@ -250,7 +260,7 @@ ZLLM_API int zllm_latent_attention_mma(const float* q_lat, const void* q, int ld
                                        const float* freq, float mag, int dims, float scale, int n_splits, int split_keys,
                                        void* stream) {
     if (T <= 0) return 0;
-    if (dims > rot || (dims & 1) || (rot % 16) || n_heads <= 0 || rot > q_off || n_splits < 1 || (n_splits > 1 && split_keys % LM_KEYS) ||
+    if (dims > rot || (dims & 1) || dims > 2 * LM_MAXHALF || (rot % 16) || n_heads <= 0 || rot > q_off || n_splits < 1 || (n_splits > 1 && split_keys % LM_KEYS) ||
         (((uintptr_t)pages | (uintptr_t)out | (uintptr_t)part_o) & 15))
         return ZLLM_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;

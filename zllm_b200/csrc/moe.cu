@@ -13,9 +13,21 @@
 
 #define MOE_MAX_E 1024
 
+// eight consecutive values as float32 (16-byte aligned for bfloat16, 32 for float32)
+__device__ __forceinline__ void moe_load8(const bf16* p, float (&v)[8]) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(h[i]); v[2 * i] = f.x; v[2 * i + 1] = f.y; }
+}
+__device__ __forceinline__ void moe_load8(const float* p, float (&v)[8]) {
+    const float4 a = reinterpret_cast<const float4*>(p)[0], b = reinterpret_cast<const float4*>(p)[1];
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+
 template <typename AT>
 __global__ void __launch_bounds__(256) moe_route_kernel(const AT* h, const AT* __restrict__ wr, int* idx, float* wt, int H,
-                                                        int E, int top, int groups, int keep) {
+                                                        int E, int top, int groups, int keep, int vec) {
     __shared__ float sc[MOE_MAX_E];
     __shared__ float gs[MOE_MAX_E];
     pdl_trigger();
@@ -26,7 +38,17 @@ __global__ void __launch_bounds__(256) moe_route_kernel(const AT* h, const AT* _
     for (int e = warp; e < E; e += nw) {
         const AT* w = wr + (size_t)e * H;
         float dot = 0.f;
-        for (int i = lane; i < H; i += 32) dot = fmaf(to_f32(hr[i]), to_f32(w[i]), dot);
+        if (vec) {                                   // pieces of eight values, a lane's pieces 256 apart
+            for (int i = lane * 8; i < H; i += 256) {
+                float a[8], b[8];
+                moe_load8(hr + i, a);
+                moe_load8(w + i, b);
+#pragma unroll
+                for (int x = 0; x < 8; ++x) dot = fmaf(a[x], b[x], dot);
+            }
+        } else {
+            for (int i = lane; i < H; i += 32) dot = fmaf(to_f32(hr[i]), to_f32(w[i]), dot);
+        }
         dot = warp_sum(dot);
         if (lane == 0) sc[e] = dot;
     }
@@ -96,11 +118,12 @@ ZLLM_API int zllm_moe_route(const void* h, const void* wr, int* idx, float* wt, 
         top > keep * (E / groups))
         return ZLLM_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
+    const int vec = (H % 8 == 0 && (((uintptr_t)h | (uintptr_t)wr) % (is_bf16 ? 16 : 32)) == 0) ? 1 : 0;
     if (is_bf16)
         return launch_pdl(moe_route_kernel<bf16>, dim3(T), dim3(256), 0, s, (const bf16*)h, (const bf16*)wr, idx, wt, H, E, top,
-                          groups, keep);
+                          groups, keep, vec);
     return launch_pdl(moe_route_kernel<float>, dim3(T), dim3(256), 0, s, (const float*)h, (const float*)wr, idx, wt, H, E, top,
-                      groups, keep);
+                      groups, keep, vec);
 }
 
 // One block.  The order of pairs inside an expert's range depends on the atomics; no result

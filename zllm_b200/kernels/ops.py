@@ -271,6 +271,7 @@ class CudaOps:
     DECODE_MAX_ROWS = 16
     LATENT_MMA_RANKS = (64, 128, 256, 512)      # latent sizes the tensor-core latent attention is built for
     LATENT_MAX_SPLITS = 32
+    LATENT_SPLIT_KEYS = 64              # the smallest split of a decoding row's keys
     EXPERT_MMA_K = 32                   # the experts' tensor-core product steps through K in pieces of 32
 
     def _gemm_decode(self, x, norm_w, eps, w, out, mode, M, N, K, rope=None):
@@ -513,9 +514,11 @@ class CudaOps:
             # few rows: their keys are divided into splits of a multiple of 256 that a second kernel merges
             n_splits, split_keys = 1, 0
             if ctx.n_decode == T:
-                need = ctx.fixed_splits or self.decode_splits(ctx.max_context)
-                n_splits = max(1, min(need, self.LATENT_MAX_SPLITS))
-                split_keys = self.decode_split_keys * -(-need // n_splits)
+                # the framework's split count (in pieces of decode_split_keys, a power of two inside graphs) bounds
+                # the context; the latent kernel cuts it finer, into at most LATENT_MAX_SPLITS splits of whole key blocks
+                reach = (ctx.fixed_splits or self.decode_splits(ctx.max_context)) * self.decode_split_keys
+                n_splits = max(1, min(self.LATENT_MAX_SPLITS, reach // self.LATENT_SPLIT_KEYS))
+                split_keys = -(-(-(-reach // n_splits)) // 32) * 32
             part_o = part_ml = None
             if n_splits > 1:
                 part_o = ctx.ws.get("latent_part_o", (T, n_heads * self.LATENT_MAX_SPLITS * rank), torch.float32, cap=T)

@@ -26,6 +26,7 @@ from .base import Mixer, StateSpec, WeightSpec, register_mixer
 class MatrixMemory(Mixer):
     capturable = True
     KERNELS = ("mlstm",)
+    FEW_ROWS = 16
 
     def __init__(self, hidden_size: int, n_heads: int, head_dim: int, value_dim: int, gate_cap: float, eps: float,
                  residual_scale: float = 1.0, init_std: float = 0.02):
@@ -81,7 +82,12 @@ class MatrixMemory(Mixer):
         qkvg = ctx.ws.get("mm_in", (T, self.w_in.shape[0]), dt)
         ops.linear(h, self.w_in, qkvg, "store")
         z = ctx.ws.get("mm_gates", (T, 2 * self.H), torch.float32)
-        ops.linear_plain(h, self.w_gates, z, "store")      # 2 * heads outputs: the plain product, float32 out
+        # 2 * heads outputs, float32: the few-row product for decode steps, the plain product otherwise
+        # (the tiled tensor-core products are made for matrices with many rows)
+        if T <= self.FEW_ROWS:
+            ops.linear(h, self.w_gates, z, "store")
+        else:
+            ops.linear_plain(h, self.w_gates, z, "store")
         out = ctx.ws.get("mm_out", (T, self.H * self.dv), dt)
         ops.matrix_memory(qkvg, self.oq, self.ok, self.ov, self.og, z, self.b_i, self.b_f, self.cap, self.norm, self.eps,
                           self.residual_scale, out, ctx, cache, self.H, self.dk, self.dv)
