@@ -1,6 +1,6 @@
 // The experts' products on tensor cores (bfloat16 operands, float32 accumulation).
 //
-// Same contract as the per-expert kernel of gemm_grouped.cu: rows are (token, choice) pairs sorted
+// Same interface as the per-expert kernel of gemm_grouped.cu: rows are (token, choice) pairs sorted
 // by expert, expert e owns the sorted range off[e]..off[e+1]-1, sorted entry i stands for pair
 // perm[i].  A CTA takes a tile of 128 sorted rows of ONE expert and 128 weight rows:
 //   first product  (swiglu): 64 gate rows and the 64 up rows of the same outputs; the rows of x are

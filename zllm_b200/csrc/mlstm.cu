@@ -10,9 +10,9 @@
 //
 // Three kernels per step of the engine:
 //   mlstm_gates:  one block per (segment, head): eight tokens at a time are staged in shared memory
-//                 (q, k, and the two gates with their tanh and logsigmoid), then one warp walks
-//                 them in order: m, n and n.q; leaves (keep, take, denominator) per (row, head)
-//                 and the new n, m.
+//                 (q, k, and the two gates with their tanh and logsigmoid) by three warps while
+//                 the first warp walks the eight before them in order: m, n and n.q; leaves
+//                 (keep, take, denominator) per (row, head) and the new n, m.
 //   mlstm_scan:   blocks per (segment, head, slice of dv): a group of lanes owns one column of S
 //                 in registers (16 rows per thread) and walks the tokens in order; q, k, v and
 //                 the per-token factors come through shared memory eight tokens at a time.
@@ -55,12 +55,12 @@ __device__ __forceinline__ void load8(const float* p, float (&v)[8]) {
 
 // Stage q (scaled) and k of tokens t0 .. t0+nc-1 of head h into dst[j * per + (0..dk-1 | dk..2dk-1)].
 // vec: pieces of eight values by 16-byte loads, several in flight per thread; else value by value.
-template <typename AT, int NTHR>
+template <typename AT>
 __device__ __forceinline__ void stage_qk(float* dst, int per, const AT* qkv, int ld, int oq, int ok, int h, int dk,
-                                         size_t t0, int nc, float qscale, int vec) {
+                                         size_t t0, int nc, float qscale, int vec, int tid, int NTHR) {
     if (vec) {
         const int pieces = 2 * dk / 8;                         // per token
-        for (int i0 = threadIdx.x; i0 < nc * pieces; i0 += NTHR * 4) {
+        for (int i0 = tid; i0 < nc * pieces; i0 += NTHR * 4) {
             float v[4][8];
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
@@ -85,7 +85,7 @@ __device__ __forceinline__ void stage_qk(float* dst, int per, const AT* qkv, int
         }
         return;
     }
-    for (int i = threadIdx.x; i < nc * 2 * dk; i += NTHR) {
+    for (int i = tid; i < nc * 2 * dk; i += NTHR) {
         const int j = i / (2 * dk), e = i - j * 2 * dk;
         dst[j * per + e] = e < dk ? to_f32(qkv[(t0 + j) * ld + oq + (size_t)h * dk + e]) * qscale
                                   : to_f32(qkv[(t0 + j) * ld + ok + (size_t)h * dk + (e - dk)]);
@@ -101,8 +101,8 @@ __global__ void __launch_bounds__(ML_GTHREADS) mlstm_gates_kernel(
     // walks the chunk: the running maximum by one lane (a chain of a few operations per token), the
     // exponentials of the chunk by eight lanes at once, n and the partial n.q token by token, and the
     // eight sums over the lanes together at the end, so that few long latencies follow one another.
-    extern __shared__ float qk_stage[];                      // [ML_CHUNK][2 * dk]
-    __shared__ float gate[ML_CHUNK][2];
+    extern __shared__ float qk_stage[];                      // [2][ML_CHUNK][2 * dk]: the chunk walked and the next one
+    __shared__ float gate2[2][ML_CHUNK][2];
     __shared__ float coef[ML_CHUNK][3];                      // keep, take, exp(-m) per token
     pdl_trigger();
     pdl_wait();
@@ -120,19 +120,32 @@ __global__ void __launch_bounds__(ML_GTHREADS) mlstm_gates_kernel(
         m = np[dk];
     }
     const float b_i = bi[h], b_f = bf[h];
-    for (int c0 = 0; c0 < rows; c0 += ML_CHUNK) {
+    // threads tid of nthr bring the chunk at c0 into buffer b: q, k, and the two log gates
+    auto produce = [&](int b, int c0, int tid, int nthr) {
         const int nc = min(ML_CHUNK, rows - c0);
-        __syncthreads();
-        stage_qk<AT, ML_GTHREADS>(qk_stage, per, qkv, ld, oq, ok, h, dk, (size_t)(row0 + c0), nc, qscale, vec);
-        if (threadIdx.x < nc) {
-            const size_t t = (size_t)(row0 + c0 + threadIdx.x);
+        stage_qk<AT>(qk_stage + (size_t)b * ML_CHUNK * per, per, qkv, ld, oq, ok, h, dk, (size_t)(row0 + c0), nc, qscale, vec,
+                     tid, nthr);
+        if (tid < nc) {
+            const size_t t = (size_t)(row0 + c0 + tid);
             const float zi = z[t * 2 * H + h], zf = z[t * 2 * H + H + h];
             const float a = cap * tanhf((zf + b_f) / cap);
-            gate[threadIdx.x][0] = cap * tanhf((zi + b_i) / cap);
-            gate[threadIdx.x][1] = fminf(a, 0.f) - log1pf(expf(-fabsf(a)));
+            gate2[b][tid][0] = cap * tanhf((zi + b_i) / cap);
+            gate2[b][tid][1] = fminf(a, 0.f) - log1pf(expf(-fabsf(a)));
         }
-        __syncthreads();
-        if (warp != 0) continue;
+    };
+    produce(0, 0, threadIdx.x, ML_GTHREADS);
+    __syncthreads();
+    int buf = 0;
+    for (int c0 = 0; c0 < rows; c0 += ML_CHUNK, buf ^= 1) {
+        const int nc = min(ML_CHUNK, rows - c0);
+        if (warp != 0) {
+            // three warps bring in the next chunk while the first walks this one
+            if (c0 + ML_CHUNK < rows) produce(buf ^ 1, c0 + ML_CHUNK, threadIdx.x - 32, ML_GTHREADS - 32);
+            __syncthreads();
+            continue;
+        }
+        const float (*gate)[2] = gate2[buf];
+        const float* qk_now = qk_stage + (size_t)buf * ML_CHUNK * per;
         // the running maximum of the chunk, token by token; every lane computes it (no exchange needed)
         float m_at[ML_CHUNK + 1];
         m_at[0] = m;
@@ -153,7 +166,7 @@ __global__ void __launch_bounds__(ML_GTHREADS) mlstm_gates_kernel(
             dot[j] = 0.f;
             if (j < nc) {
                 const float keep = coef[j][0], take = coef[j][1];
-                const float* q = qk_stage + j * per;
+                const float* q = qk_now + j * per;
                 const float* k = q + dk;
 #pragma unroll
                 for (int i = 0; i < ML_NL; ++i) {
@@ -175,6 +188,7 @@ __global__ void __launch_bounds__(ML_GTHREADS) mlstm_gates_kernel(
                 float* f = fac + ((size_t)(row0 + c0 + j) * H + h) * 4;
                 f[0] = coef[j][0]; f[1] = coef[j][1]; f[2] = fmaxf(fabsf(dot[j]), coef[j][2]) + 1e-6f;
             }
+        __syncthreads();                                  // the next chunk is in place, this one may be overwritten
     }
     if (warp != 0) return;
 #pragma unroll
@@ -186,33 +200,38 @@ __global__ void __launch_bounds__(ML_GTHREADS) mlstm_gates_kernel(
 #define ML_COLT 256       // threads of a scan block
 #define ML_RPT 16         // rows of S per thread
 
+#define ML_PROD 64        // threads of a scan block that only bring in the next chunk
+
 template <typename AT>
-__global__ void __launch_bounds__(ML_COLT) mlstm_scan_kernel(
+__global__ void __launch_bounds__(ML_COLT + ML_PROD) mlstm_scan_kernel(
     const AT* qkv, int ld, int oq, int ok, int ov, const float* fac, float qscale, const int* __restrict__ segs,
     const int* row_slot, float* state, size_t state_stride, float* out, int H, int dk, int dv, int kp, int vec) {
     // kp lanes share a column of S (rows sub, sub + kp, ...: ML_RPT of them per thread), so that a step is
-    // short and an SM holds many warps; the lanes' partial sums are added with shuffles.
-    extern __shared__ float sm[];
+    // short and an SM holds many warps; the lanes' partial sums are added with shuffles.  Two more warps
+    // bring the next eight tokens into the other half of shared memory while these are walked.
+    extern __shared__ float sm[];                     // [2][ML_CHUNK][per]
     pdl_trigger();
     pdl_wait();
     const int h = blockIdx.y;
     int row0, rows, slot;
     if (!segment_of(segs, row_slot, blockIdx.x, row0, rows, slot)) return;
+    const int tidx = threadIdx.x;
+    const bool producer = tidx >= ML_COLT;
     const int vs = ML_COLT / kp;                      // columns of this block
-    const int sub = threadIdx.x % kp;
-    const int lcol = threadIdx.x / kp;
+    const int sub = tidx % kp;
+    const int lcol = producer ? 0 : tidx / kp;
     const int col = blockIdx.z * vs + lcol;
-    const bool has = col < dv;
+    const bool has = !producer && col < dv;
     float* S = state + (size_t)slot * state_stride + (size_t)h * ((size_t)dk * dv + dk + 1);
     float s[ML_RPT];
 #pragma unroll
     for (int i = 0; i < ML_RPT; ++i) { const int r = sub + i * kp; s[i] = (has && r < dk) ? S[(size_t)r * dv + col] : 0.f; }
     const int per = 2 * dk + vs + 4;                  // floats staged per token: q, k, v slice, factors
-    for (int c0 = 0; c0 < rows; c0 += ML_CHUNK) {
+    auto produce = [&](int b, int c0, int tid, int nthr) {
         const int nc = min(ML_CHUNK, rows - c0);
-        __syncthreads();
-        stage_qk<AT, ML_COLT>(sm, per, qkv, ld, oq, ok, h, dk, (size_t)(row0 + c0), nc, qscale, vec);
-        for (int i = threadIdx.x; i < nc * (vs + 4); i += ML_COLT) {
+        float* dst = sm + (size_t)b * ML_CHUNK * per;
+        stage_qk<AT>(dst, per, qkv, ld, oq, ok, h, dk, (size_t)(row0 + c0), nc, qscale, vec, tid, nthr);
+        for (int i = tid; i < nc * (vs + 4); i += nthr) {
             const int j = i / (vs + 4), e = i - j * (vs + 4);
             const size_t t = (size_t)(row0 + c0 + j);
             float v;
@@ -220,28 +239,39 @@ __global__ void __launch_bounds__(ML_COLT) mlstm_scan_kernel(
                 const int cc = blockIdx.z * vs + e;
                 v = cc < dv ? to_f32(qkv[t * ld + ov + (size_t)h * dv + cc]) : 0.f;
             } else v = fac[(t * H + h) * 4 + (e - vs)];
-            sm[j * per + 2 * dk + e] = v;
+            dst[j * per + 2 * dk + e] = v;
         }
-        __syncthreads();
-        for (int j = 0; j < nc; ++j) {
-            const float* q = sm + j * per;
-            const float* k = q + dk;
-            const float vv = q[2 * dk + lcol];
-            const float keep = q[2 * dk + vs], take = q[2 * dk + vs + 1], den = q[2 * dk + vs + 2];
-            const float tv = take * vv;
-            float part[4] = {0.f, 0.f, 0.f, 0.f};         // four chains instead of one of dependent additions
+    };
+    produce(0, 0, tidx, ML_COLT + ML_PROD);
+    __syncthreads();
+    int buf = 0;
+    for (int c0 = 0; c0 < rows; c0 += ML_CHUNK, buf ^= 1) {
+        const int nc = min(ML_CHUNK, rows - c0);
+        if (producer) {
+            if (c0 + ML_CHUNK < rows) produce(buf ^ 1, c0 + ML_CHUNK, tidx - ML_COLT, ML_PROD);
+        } else {
+            const float* now = sm + (size_t)buf * ML_CHUNK * per;
+            for (int j = 0; j < nc; ++j) {
+                const float* q = now + j * per;
+                const float* k = q + dk;
+                const float vv = q[2 * dk + lcol];
+                const float keep = q[2 * dk + vs], take = q[2 * dk + vs + 1], den = q[2 * dk + vs + 2];
+                const float tv = take * vv;
+                float part[4] = {0.f, 0.f, 0.f, 0.f};     // four chains instead of one of dependent additions
 #pragma unroll
-            for (int i = 0; i < ML_RPT; ++i) {
-                const int r = sub + i * kp;
-                if (r < dk) {
-                    s[i] = fmaf(tv, k[r], keep * s[i]);
-                    part[i & 3] = fmaf(s[i], q[r], part[i & 3]);
+                for (int i = 0; i < ML_RPT; ++i) {
+                    const int r = sub + i * kp;
+                    if (r < dk) {
+                        s[i] = fmaf(tv, k[r], keep * s[i]);
+                        part[i & 3] = fmaf(s[i], q[r], part[i & 3]);
+                    }
                 }
+                float num = (part[0] + part[1]) + (part[2] + part[3]);
+                for (int o = 1; o < kp; o <<= 1) num += __shfl_xor_sync(0xffffffffu, num, o);
+                if (has && sub == 0) out[(size_t)(row0 + c0 + j) * H * dv + (size_t)h * dv + col] = num / den;
             }
-            float num = (part[0] + part[1]) + (part[2] + part[3]);
-            for (int o = 1; o < kp; o <<= 1) num += __shfl_xor_sync(0xffffffffu, num, o);
-            if (has && sub == 0) out[(size_t)(row0 + c0 + j) * H * dv + (size_t)h * dv + col] = num / den;
         }
+        __syncthreads();                              // the next chunk is in place, this one may be overwritten
     }
     if (has) {
 #pragma unroll
@@ -291,8 +321,17 @@ ZLLM_API int zllm_mlstm(const void* qkv, int ld, int oq, int ok, int ov, int og,
     int kp = 1;
     while (kp * ML_RPT < dk) kp *= 2;                 // lanes per column of S: ML_RPT rows per thread, at most 32 lanes
     const int vs = ML_COLT / kp;
-    const size_t smem = (size_t)ML_CHUNK * (2 * dk + vs + 4) * sizeof(float);
-    const size_t gsmem = (size_t)ML_CHUNK * 2 * dk * sizeof(float);
+    const size_t smem = (size_t)2 * ML_CHUNK * (2 * dk + vs + 4) * sizeof(float);     // two chunks: walked, and brought in
+    const size_t gsmem = (size_t)2 * ML_CHUNK * 2 * dk * sizeof(float);
+    static bool raised = false;
+    if (!raised) {                                    // dk = 512 needs 66 KB of dynamic shared memory
+        cudaError_t e = cudaFuncSetAttribute(mlstm_gates_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 72 * 1024);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(mlstm_gates_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 72 * 1024);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(mlstm_scan_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 72 * 1024);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(mlstm_scan_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 72 * 1024);
+        if (e != cudaSuccess) return (int)e;
+        raised = true;
+    }
     dim3 grid(ns, H, (dv + vs - 1) / vs);
     // pieces of eight values by 16-byte loads when every run of q and k starts on such a boundary
     const int el = is_bf16 ? 2 : 4;
@@ -303,13 +342,13 @@ ZLLM_API int zllm_mlstm(const void* qkv, int ld, int oq, int ok, int ov, int og,
             code = launch_pdl(mlstm_gates_kernel<bf16>, dim3(ns, H), dim3(ML_GTHREADS), gsmem, s, (const bf16*)qkv, ld, oq, ok, z,
                               bi, bf, cap, qscale, segs, row_slot, state, (size_t)state_stride, fac, H, dk, dv, vec);
             if (code) return code;
-            code = launch_pdl(mlstm_scan_kernel<bf16>, grid, dim3(ML_COLT), smem, s, (const bf16*)qkv, ld, oq, ok, ov, fac,
+            code = launch_pdl(mlstm_scan_kernel<bf16>, grid, dim3(ML_COLT + ML_PROD), smem, s, (const bf16*)qkv, ld, oq, ok, ov, fac,
                               qscale, segs, row_slot, state, (size_t)state_stride, raw, H, dk, dv, kp, vec);
         } else {
             code = launch_pdl(mlstm_gates_kernel<float>, dim3(ns, H), dim3(ML_GTHREADS), gsmem, s, (const float*)qkv, ld, oq, ok,
                               z, bi, bf, cap, qscale, segs, row_slot, state, (size_t)state_stride, fac, H, dk, dv, vec);
             if (code) return code;
-            code = launch_pdl(mlstm_scan_kernel<float>, grid, dim3(ML_COLT), smem, s, (const float*)qkv, ld, oq, ok, ov, fac,
+            code = launch_pdl(mlstm_scan_kernel<float>, grid, dim3(ML_COLT + ML_PROD), smem, s, (const float*)qkv, ld, oq, ok, ov, fac,
                               qscale, segs, row_slot, state, (size_t)state_stride, raw, H, dk, dv, kp, vec);
         }
         if (code) return code;
