@@ -77,11 +77,13 @@ __global__ void __launch_bounds__(256) gemm_experts_mma_kernel(const bf16* x, co
     const bf16* a_src[PER_THREAD];
     const bf16* b_src[PER_THREAD];
     int dst[PER_THREAD];
+    bool a_live[PER_THREAD];
 #pragma unroll
     for (int i = 0; i < PER_THREAD; ++i) {
         const int c = tid + i * 256, r = c / PIECES, kc = c % PIECES;
         int ri = row0 + r;
-        if (ri >= row_end) ri = row0;                        // rows beyond the expert's range repeat a real one; never stored
+        a_live[i] = ri < row_end;                            // rows beyond the expert's range are neither loaded nor stored:
+        if (ri >= row_end) ri = row0;                        // what a product makes of them stays in rows nobody reads
         const size_t src = SWIGLU ? (size_t)(perm[ri] / top) : (size_t)ri;
         a_src[i] = x + src * K + kc * 8;
         int n;
@@ -95,7 +97,7 @@ __global__ void __launch_bounds__(256) gemm_experts_mma_kernel(const bf16* x, co
     auto load_stage = [&](int st, int kt) {
 #pragma unroll
         for (int i = 0; i < PER_THREAD; ++i) {
-            cp_async16(As + st * TM * LDS + dst[i], a_src[i] + (size_t)kt * TK);
+            if (a_live[i]) cp_async16(As + st * TM * LDS + dst[i], a_src[i] + (size_t)kt * TK);
             cp_async16(Bs + st * TN * LDS + dst[i], b_src[i] + (size_t)kt * TK);
         }
     };
@@ -108,6 +110,7 @@ __global__ void __launch_bounds__(256) gemm_experts_mma_kernel(const bf16* x, co
             for (int c = 0; c < 4; ++c) acc[a][b][c] = 0.f;
 
     const int KT = K / TK;
+    const bool warp_live = row0 + wm * 32 < row_end;
 #pragma unroll
     for (int s = 0; s < STAGES - 1; ++s) {
         if (s < KT) load_stage(s, s);
@@ -120,6 +123,7 @@ __global__ void __launch_bounds__(256) gemm_experts_mma_kernel(const bf16* x, co
         cp_async_commit();
         const bf16* Ast = As + (kt % STAGES) * TM * LDS;
         const bf16* Bst = Bs + (kt % STAGES) * TN * LDS;
+        if (!warp_live) continue;                            // this warp's 32 rows lie beyond the expert's range (few rows)
 #pragma unroll
         for (int ks = 0; ks < TK / 16; ++ks) {
             unsigned af[2][4];
