@@ -142,9 +142,10 @@ def test_experts(ops, dtype, T, H, F, E, top):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_products_per_head(ops, dtype):
+@pytest.mark.parametrize("T,G,N,K,stride", [(75, 5, 40, 24, 40), (300, 3, 200, 64, 72), (9, 4, 136, 128, 128)])
+def test_products_per_head(ops, dtype, T, G, N, K, stride):
+    # K a multiple of 32 with strides of eight reaches the tensor-core kernel in bfloat16
     g = torch.Generator().manual_seed(3)
-    T, G, N, K, stride = 75, 5, 40, 24, 40
     x = torch.randn(T, G * stride, generator=g).to(dtype)
     w = (torch.randn(G, N, K, generator=g) * 0.3).to(dtype)
     gate = torch.randn(T, 16 + G * N, generator=g).to(dtype)

@@ -1,4 +1,4 @@
-// The experts' products on tensor cores (bfloat16 operands, float32 accumulation).
+// The experts' products, and the per-head products, on tensor cores (bfloat16 operands, float32 accumulation).
 //
 // Same interface as the per-expert kernel of gemm_grouped.cu: rows are (token, choice) pairs sorted
 // by expert, expert e owns the sorted range off[e]..off[e+1]-1, sorted entry i stands for pair
@@ -26,6 +26,65 @@ __device__ __forceinline__ void cp_async16(void* dst, const void* src) {
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
 template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+// The product of one tile: A rows and B rows arrive through the cp.async ring, PER_THREAD 16-byte pieces of
+// each per thread and stage (a_src / b_src: where the thread's pieces start in global memory, dst: where
+// they go in a stage, a_live: whether the A row exists); acc[mt][nt] are the warp's 2 x 8 tiles of 16 x 8.
+template <bool SWIGLU, int TK, int STAGES, int PER_THREAD>
+__device__ __forceinline__ void tile_mainloop(bf16* As, bf16* Bs, const bf16* (&a_src)[PER_THREAD], const bf16* (&b_src)[PER_THREAD],
+                                              const bool (&a_live)[PER_THREAD], const int (&dst)[PER_THREAD], int K, bool warp_live,
+                                              int wm, int wn, int lane, float (&acc)[2][8][4]) {
+    constexpr int LDS = TK + 8;
+    auto load_stage = [&](int st, int kt) {
+#pragma unroll
+        for (int i = 0; i < PER_THREAD; ++i) {
+            if (a_live[i]) cp_async16(As + st * TM * LDS + dst[i], a_src[i] + (size_t)kt * TK);
+            cp_async16(Bs + st * TN * LDS + dst[i], b_src[i] + (size_t)kt * TK);
+        }
+    };
+#pragma unroll
+    for (int a = 0; a < 2; ++a)
+#pragma unroll
+        for (int b = 0; b < 8; ++b)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) acc[a][b][c] = 0.f;
+
+    const int KT = K / TK;
+#pragma unroll
+    for (int s = 0; s < STAGES - 1; ++s) {
+        if (s < KT) load_stage(s, s);
+        cp_async_commit();
+    }
+    for (int kt = 0; kt < KT; ++kt) {
+        cp_async_wait<STAGES - 2>();
+        __syncthreads();
+        if (kt + STAGES - 1 < KT) load_stage((kt + STAGES - 1) % STAGES, kt + STAGES - 1);
+        cp_async_commit();
+        const bf16* Ast = As + (kt % STAGES) * TM * LDS;
+        const bf16* Bst = Bs + (kt % STAGES) * TN * LDS;
+        if (!warp_live) continue;                            // this warp's 32 rows lie beyond the expert's range (few rows)
+#pragma unroll
+        for (int ks = 0; ks < TK / 16; ++ks) {
+            unsigned af[2][4];
+#pragma unroll
+            for (int mt = 0; mt < 2; ++mt)
+                ldmatrix_x4(af[mt], Ast + (wm * 32 + mt * 16 + (lane & 15)) * LDS + ks * 16 + (lane >> 4) * 8);
+#pragma unroll
+            for (int p = 0; p < 4; ++p) {
+                // 16 weight rows per ldmatrix: with SWIGLU the warp's first 32 are gate rows, the last 32 their up rows
+                const int brow = SWIGLU ? (p < 2 ? wn * 32 + p * 16 : 64 + wn * 32 + (p - 2) * 16) : wn * 64 + p * 16;
+                unsigned bfr[4];
+                ldmatrix_x4(bfr, Bst + (brow + (lane & 7) + (lane >> 4) * 8) * LDS + ks * 16 + ((lane >> 3) & 1) * 8);
+#pragma unroll
+                for (int mt = 0; mt < 2; ++mt) {
+                    mma16816(acc[mt][2 * p], af[mt], bfr[0], bfr[1]);
+                    mma16816(acc[mt][2 * p + 1], af[mt], bfr[2], bfr[3]);
+                }
+            }
+        }
+    }
+    cp_async_wait<0>();
+}
 
 template <bool SWIGLU, int TK, int STAGES>
 __global__ void __launch_bounds__(256) gemm_experts_mma_kernel(const bf16* x, const bf16* __restrict__ w,
@@ -94,57 +153,9 @@ __global__ void __launch_bounds__(256) gemm_experts_mma_kernel(const bf16* x, co
         b_src[i] = base + (size_t)n * K + kc * 8;
         dst[i] = r * LDS + kc * 8;
     }
-    auto load_stage = [&](int st, int kt) {
-#pragma unroll
-        for (int i = 0; i < PER_THREAD; ++i) {
-            if (a_live[i]) cp_async16(As + st * TM * LDS + dst[i], a_src[i] + (size_t)kt * TK);
-            cp_async16(Bs + st * TN * LDS + dst[i], b_src[i] + (size_t)kt * TK);
-        }
-    };
     float acc[2][8][4];
-#pragma unroll
-    for (int a = 0; a < 2; ++a)
-#pragma unroll
-        for (int b = 0; b < 8; ++b)
-#pragma unroll
-            for (int c = 0; c < 4; ++c) acc[a][b][c] = 0.f;
-
-    const int KT = K / TK;
     const bool warp_live = row0 + wm * 32 < row_end;
-#pragma unroll
-    for (int s = 0; s < STAGES - 1; ++s) {
-        if (s < KT) load_stage(s, s);
-        cp_async_commit();
-    }
-    for (int kt = 0; kt < KT; ++kt) {
-        cp_async_wait<STAGES - 2>();
-        __syncthreads();
-        if (kt + STAGES - 1 < KT) load_stage((kt + STAGES - 1) % STAGES, kt + STAGES - 1);
-        cp_async_commit();
-        const bf16* Ast = As + (kt % STAGES) * TM * LDS;
-        const bf16* Bst = Bs + (kt % STAGES) * TN * LDS;
-        if (!warp_live) continue;                            // this warp's 32 rows lie beyond the expert's range (few rows)
-#pragma unroll
-        for (int ks = 0; ks < TK / 16; ++ks) {
-            unsigned af[2][4];
-#pragma unroll
-            for (int mt = 0; mt < 2; ++mt)
-                ldmatrix_x4(af[mt], Ast + (wm * 32 + mt * 16 + (lane & 15)) * LDS + ks * 16 + (lane >> 4) * 8);
-#pragma unroll
-            for (int p = 0; p < 4; ++p) {
-                // 16 weight rows per ldmatrix: with SWIGLU the warp's first 32 are gate rows, the last 32 their up rows
-                const int brow = SWIGLU ? (p < 2 ? wn * 32 + p * 16 : 64 + wn * 32 + (p - 2) * 16) : wn * 64 + p * 16;
-                unsigned bfr[4];
-                ldmatrix_x4(bfr, Bst + (brow + (lane & 7) + (lane >> 4) * 8) * LDS + ks * 16 + ((lane >> 3) & 1) * 8);
-#pragma unroll
-                for (int mt = 0; mt < 2; ++mt) {
-                    mma16816(acc[mt][2 * p], af[mt], bfr[0], bfr[1]);
-                    mma16816(acc[mt][2 * p + 1], af[mt], bfr[2], bfr[3]);
-                }
-            }
-        }
-    }
-    cp_async_wait<0>();
+    tile_mainloop<SWIGLU, TK, STAGES, PER_THREAD>(As, Bs, a_src, b_src, a_live, dst, K, warp_live, wm, wn, lane, acc);
     // epilogue: thread holds rows lane/4 (+8) and columns 2*(lane%4), +1 of every 16x8 tile
 #pragma unroll
     for (int mt = 0; mt < 2; ++mt)
@@ -204,4 +215,88 @@ ZLLM_API int zllm_gemm_experts_mma(const void* x, const void* w, const void* wu,
     if (few) GE_GO(false, 64, 3);
     GE_GO(false, 32, 3);
 #undef GE_GO
+}
+
+// ---------------------------------------------------------------- per head
+// out[t][g*N + n] = x[t][g*xg : g*xg + K] . w[g][n], optionally times sigmoid(gate[t][g*N + n]) * out_scale:
+// the per-head products of gemm_grouped.cu on tensor cores.  Tile (n tile, 128 rows of the step, head).
+template <bool OUT_F32, int TK, int STAGES>
+__global__ void __launch_bounds__(256) gemm_heads_mma_kernel(const bf16* x, int ldx, int xg, const bf16* __restrict__ w, void* out,
+                                                             const bf16* gate, int ldg, float out_scale, int T, int N, int K,
+                                                             int G) {
+    constexpr int LDS = TK + 8, PIECES = TK / 8, PER_THREAD = TM * PIECES / 256;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    bf16* As = reinterpret_cast<bf16*>(smem_raw);
+    bf16* Bs = As + STAGES * TM * LDS;
+    pdl_trigger();
+    pdl_wait();
+    const int g = blockIdx.z, row0 = blockIdx.y * TM, row_end = T, n0 = blockIdx.x * TN;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int wm = warp >> 1, wn = warp & 1;
+    const bf16* a_src[PER_THREAD];
+    const bf16* b_src[PER_THREAD];
+    int dst[PER_THREAD];
+    bool a_live[PER_THREAD];
+#pragma unroll
+    for (int i = 0; i < PER_THREAD; ++i) {
+        const int c = tid + i * 256, r = c / PIECES, kc = c % PIECES;
+        int ri = row0 + r;
+        a_live[i] = ri < row_end;
+        if (ri >= row_end) ri = row0;
+        a_src[i] = x + (size_t)ri * ldx + (size_t)g * xg + kc * 8;
+        int n = n0 + r;
+        if (n >= N) n = N - 1;
+        b_src[i] = w + ((size_t)g * N + n) * K + kc * 8;
+        dst[i] = r * LDS + kc * 8;
+    }
+    float acc[2][8][4];
+    const bool warp_live = row0 + wm * 32 < row_end;
+    tile_mainloop<false, TK, STAGES, PER_THREAD>(As, Bs, a_src, b_src, a_live, dst, K, warp_live, wm, wn, lane, acc);
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int r = row0 + wm * 32 + mt * 16 + (lane >> 2) + half * 8;
+            if (r >= row_end) continue;
+#pragma unroll
+            for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+                    const int n = n0 + wn * 64 + nt * 8 + 2 * (lane & 3) + c;
+                    if (n >= N) continue;
+                    float v = acc[mt][nt][half * 2 + c];
+                    if (gate != nullptr) v = v * (1.f / (1.f + expf(-to_f32(gate[(size_t)r * ldg + (size_t)g * N + n])))) * out_scale;
+                    const size_t o = ((size_t)r * G + g) * N + n;
+                    if (OUT_F32) reinterpret_cast<float*>(out)[o] = v;
+                    else reinterpret_cast<bf16*>(out)[o] = __float2bfloat16_rn(v);
+                }
+        }
+}
+
+// As zllm_gemm_heads (gemm_grouped.cu) for bfloat16 x, w and gate; out float32 or bfloat16.
+ZLLM_API int zllm_gemm_heads_mma(const void* x, int ldx, int xg, const void* w, void* out, const void* gate, int ldg,
+                                 float out_scale, int T, int N, int K, int G, int out_f32, void* stream) {
+    if (T <= 0 || N <= 0 || G <= 0) return 0;
+    if (K <= 0 || (K % 32) || (ldx % 8) || (xg % 8) || (((uintptr_t)x | (uintptr_t)w) & 15)) return ZLLM_ERR_UNSUPPORTED;
+    cudaStream_t s = (cudaStream_t)stream;
+    const bool few = T <= 256 && K % 64 == 0;
+    const size_t smem = few ? (size_t)3 * (TM + TN) * 72 * sizeof(bf16) : (size_t)3 * (TM + TN) * 40 * sizeof(bf16);
+    static bool raised = false;
+    if (!raised) {
+        const int big = 3 * (TM + TN) * 72 * (int)sizeof(bf16), small = 3 * (TM + TN) * 40 * (int)sizeof(bf16);
+        cudaError_t e = cudaFuncSetAttribute(gemm_heads_mma_kernel<true, 32, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, small);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_heads_mma_kernel<false, 32, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, small);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_heads_mma_kernel<true, 64, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_heads_mma_kernel<false, 64, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
+        if (e != cudaSuccess) return (int)e;
+        raised = true;
+    }
+    dim3 grid((N + TN - 1) / TN, (T + TM - 1) / TM, G);
+#define GH_GO(F32, TKV) return launch_pdl(gemm_heads_mma_kernel<F32, TKV, 3>, grid, dim3(256), smem, s, (const bf16*)x, ldx, xg, \
+                                          (const bf16*)w, out, (const bf16*)gate, ldg, out_scale, T, N, K, G)
+    if (out_f32 && few) GH_GO(true, 64);
+    if (out_f32) GH_GO(true, 32);
+    if (few) GH_GO(false, 64);
+    GH_GO(false, 32);
+#undef GH_GO
 }

@@ -553,6 +553,13 @@ class CudaOps:
         if tuple(out.shape) != (T, G * N) or (G - 1) * x_head_stride + K > x.shape[1] \
                 or x.dtype not in (w.dtype, torch.float32) or out.dtype not in (w.dtype, torch.float32):
             raise BackendError("linear_heads: bad operand types or shapes")
+        if w.dtype == torch.bfloat16 and x.dtype == torch.bfloat16 and K % self.EXPERT_MMA_K == 0 and x.shape[1] % 8 == 0 \
+                and x_head_stride % 8 == 0 and (x.data_ptr() | w.data_ptr()) & 15 == 0:
+            code = self.lib("gemm_grouped_mma").zllm_gemm_heads_mma(
+                _ptr(x), c_int(x.shape[1]), c_int(x_head_stride), _ptr(w), _ptr(out), gptr, c_int(ldg), c_float(out_scale), c_int(T),
+                c_int(N), c_int(K), c_int(G), c_int(out.dtype == torch.float32), self._stream())
+            self._check(code, "gemm_heads_mma")
+            return
         code = self.lib("gemm_grouped").zllm_gemm_heads(
             _ptr(x), c_int(x.shape[1]), c_int(x_head_stride), _ptr(w), _ptr(out), gptr, c_int(ldg), c_float(out_scale), c_int(T),
             c_int(N), c_int(K), c_int(G), c_int(w.dtype == torch.bfloat16), c_int(x.dtype == torch.float32),

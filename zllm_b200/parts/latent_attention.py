@@ -75,7 +75,8 @@ class LatentAttention(Mixer):
         prepare = getattr(rt.ops, "prepare", None)
         if prepare is not None:
             mma = rt.dtype == torch.bfloat16 and self.kv_rank in getattr(rt.ops, "LATENT_MMA_RANKS", ()) and self.dr % 16 == 0
-            prepare(self.KERNELS + (("latent_attention_mma",) if mma else ()))
+            prepare(self.KERNELS + (("latent_attention_mma",) if mma else ())
+                    + (("gemm_grouped_mma",) if rt.dtype == torch.bfloat16 and self.dn % 32 == 0 else ()))
 
     def load(self, tensors):
         H = self.H
