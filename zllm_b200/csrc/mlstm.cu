@@ -92,7 +92,8 @@ __device__ __forceinline__ void stage_qk(float* dst, int per, const AT* qkv, int
     }
 }
 
-template <typename AT>
+// NLT > 0: dk is exactly 32 * NLT (no bounds checks, no idle registers); NLT == 0: any dk up to 32 * ML_NL.
+template <typename AT, int NLT>
 __global__ void __launch_bounds__(ML_GTHREADS) mlstm_gates_kernel(
     const AT* qkv, int ld, int oq, int ok, const float* z, const float* __restrict__ bi, const float* __restrict__ bf,
     float cap, float qscale, const int* __restrict__ segs, const int* row_slot, float* state, size_t state_stride,
@@ -112,11 +113,12 @@ __global__ void __launch_bounds__(ML_GTHREADS) mlstm_gates_kernel(
     const int per = 2 * dk;
     float* st = state + (size_t)slot * state_stride + (size_t)h * ((size_t)dk * dv + dk + 1);
     float* np = st + (size_t)dk * dv;
-    float n[ML_NL];
+    constexpr int NLV = NLT > 0 ? NLT : ML_NL;
+    float n[NLV];
     float m = 0.f;
     if (warp == 0) {
 #pragma unroll
-        for (int i = 0; i < ML_NL; ++i) { const int r = lane + 32 * i; n[i] = r < dk ? np[r] : 0.f; }
+        for (int i = 0; i < NLV; ++i) { const int r = lane + 32 * i; n[i] = (NLT > 0 || r < dk) ? np[r] : 0.f; }
         m = np[dk];
     }
     const float b_i = bi[h], b_f = bf[h];
@@ -169,9 +171,9 @@ __global__ void __launch_bounds__(ML_GTHREADS) mlstm_gates_kernel(
                 const float* q = qk_now + j * per;
                 const float* k = q + dk;
 #pragma unroll
-                for (int i = 0; i < ML_NL; ++i) {
+                for (int i = 0; i < NLV; ++i) {
                     const int r = lane + 32 * i;
-                    if (r < dk) {
+                    if (NLT > 0 || r < dk) {
                         n[i] = keep * n[i] + take * k[r];
                         dot[j] = fmaf(n[i], q[r], dot[j]);
                     }
@@ -192,7 +194,7 @@ __global__ void __launch_bounds__(ML_GTHREADS) mlstm_gates_kernel(
     }
     if (warp != 0) return;
 #pragma unroll
-    for (int i = 0; i < ML_NL; ++i) { const int r = lane + 32 * i; if (r < dk) np[r] = n[i]; }
+    for (int i = 0; i < NLV; ++i) { const int r = lane + 32 * i; if (NLT > 0 || r < dk) np[r] = n[i]; }
     if (lane == 0) np[dk] = m;
 }
 
@@ -202,7 +204,8 @@ __global__ void __launch_bounds__(ML_GTHREADS) mlstm_gates_kernel(
 
 #define ML_PROD 64        // threads of a scan block that only bring in the next chunk
 
-template <typename AT>
+// KPT > 0: kp is KPT and dk exactly KPT * ML_RPT (offsets known to the compiler, no bounds checks); 0: any.
+template <typename AT, int KPT>
 __global__ void __launch_bounds__(ML_COLT + ML_PROD) mlstm_scan_kernel(
     const AT* qkv, int ld, int oq, int ok, int ov, const float* fac, float qscale, const int* __restrict__ segs,
     const int* row_slot, float* state, size_t state_stride, float* out, int H, int dk, int dv, int kp, int vec) {
@@ -212,6 +215,7 @@ __global__ void __launch_bounds__(ML_COLT + ML_PROD) mlstm_scan_kernel(
     extern __shared__ float sm[];                     // [2][ML_CHUNK][per]
     pdl_trigger();
     pdl_wait();
+    if (KPT > 0) { kp = KPT; dk = KPT * ML_RPT; }
     const int h = blockIdx.y;
     int row0, rows, slot;
     if (!segment_of(segs, row_slot, blockIdx.x, row0, rows, slot)) return;
@@ -225,7 +229,7 @@ __global__ void __launch_bounds__(ML_COLT + ML_PROD) mlstm_scan_kernel(
     float* S = state + (size_t)slot * state_stride + (size_t)h * ((size_t)dk * dv + dk + 1);
     float s[ML_RPT];
 #pragma unroll
-    for (int i = 0; i < ML_RPT; ++i) { const int r = sub + i * kp; s[i] = (has && r < dk) ? S[(size_t)r * dv + col] : 0.f; }
+    for (int i = 0; i < ML_RPT; ++i) { const int r = sub + i * kp; s[i] = (has && (KPT > 0 || r < dk)) ? S[(size_t)r * dv + col] : 0.f; }
     const int per = 2 * dk + vs + 4;                  // floats staged per token: q, k, v slice, factors
     auto produce = [&](int b, int c0, int tid, int nthr) {
         const int nc = min(ML_CHUNK, rows - c0);
@@ -261,7 +265,7 @@ __global__ void __launch_bounds__(ML_COLT + ML_PROD) mlstm_scan_kernel(
 #pragma unroll
                 for (int i = 0; i < ML_RPT; ++i) {
                     const int r = sub + i * kp;
-                    if (r < dk) {
+                    if (KPT > 0 || r < dk) {
                         s[i] = fmaf(tv, k[r], keep * s[i]);
                         part[i & 3] = fmaf(s[i], q[r], part[i & 3]);
                     }
@@ -275,7 +279,7 @@ __global__ void __launch_bounds__(ML_COLT + ML_PROD) mlstm_scan_kernel(
     }
     if (has) {
 #pragma unroll
-        for (int i = 0; i < ML_RPT; ++i) { const int r = sub + i * kp; if (r < dk) S[(size_t)r * dv + col] = s[i]; }
+        for (int i = 0; i < ML_RPT; ++i) { const int r = sub + i * kp; if (KPT > 0 || r < dk) S[(size_t)r * dv + col] = s[i]; }
     }
 }
 
@@ -323,36 +327,47 @@ ZLLM_API int zllm_mlstm(const void* qkv, int ld, int oq, int ok, int ov, int og,
     const int vs = ML_COLT / kp;
     const size_t smem = (size_t)2 * ML_CHUNK * (2 * dk + vs + 4) * sizeof(float);     // two chunks: walked, and brought in
     const size_t gsmem = (size_t)2 * ML_CHUNK * 2 * dk * sizeof(float);
-    static bool raised = false;
-    if (!raised) {                                    // dk = 512 needs 66 KB of dynamic shared memory
-        cudaError_t e = cudaFuncSetAttribute(mlstm_gates_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 72 * 1024);
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(mlstm_gates_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 72 * 1024);
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(mlstm_scan_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 72 * 1024);
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(mlstm_scan_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 72 * 1024);
-        if (e != cudaSuccess) return (int)e;
-        raised = true;
-    }
     dim3 grid(ns, H, (dv + vs - 1) / vs);
     // pieces of eight values by 16-byte loads when every run of q and k starts on such a boundary
     const int el = is_bf16 ? 2 : 4;
     const int vec = (dk % 8 == 0 && ld % 8 == 0 && oq % 8 == 0 && ok % 8 == 0 && ((uintptr_t)qkv % (8 * el)) == 0) ? 1 : 0;
+    // the kernels are instantiated for the sizes that fill their registers exactly (dk = 32 * 2^a for the
+    // gates, dk = 16 * kp for the scan) and once for any size
+#define ML_LAUNCH(AT)                                                                                                         \
+    do {                                                                                                                      \
+        auto gk = mlstm_gates_kernel<AT, 0>;                                                                                  \
+        if (dk == 32) gk = mlstm_gates_kernel<AT, 1>;                                                                         \
+        else if (dk == 64) gk = mlstm_gates_kernel<AT, 2>;                                                                    \
+        else if (dk == 128) gk = mlstm_gates_kernel<AT, 4>;                                                                   \
+        else if (dk == 256) gk = mlstm_gates_kernel<AT, 8>;                                                                   \
+        else if (dk == 512) gk = mlstm_gates_kernel<AT, 16>;                                                                  \
+        auto sk = mlstm_scan_kernel<AT, 0>;                                                                                   \
+        if (dk == kp * ML_RPT) {                                                                                              \
+            if (kp == 1) sk = mlstm_scan_kernel<AT, 1>;                                                                       \
+            else if (kp == 2) sk = mlstm_scan_kernel<AT, 2>;                                                                  \
+            else if (kp == 4) sk = mlstm_scan_kernel<AT, 4>;                                                                  \
+            else if (kp == 8) sk = mlstm_scan_kernel<AT, 8>;                                                                  \
+            else if (kp == 16) sk = mlstm_scan_kernel<AT, 16>;                                                                \
+            else if (kp == 32) sk = mlstm_scan_kernel<AT, 32>;                                                                \
+        }                                                                                                                     \
+        if (smem > 48 * 1024 || gsmem > 48 * 1024) {        /* dk = 512 needs 66 KB of dynamic shared memory */              \
+            cudaError_t e = cudaFuncSetAttribute(gk, cudaFuncAttributeMaxDynamicSharedMemorySize, 72 * 1024);                 \
+            if (e == cudaSuccess) e = cudaFuncSetAttribute(sk, cudaFuncAttributeMaxDynamicSharedMemorySize, 72 * 1024);       \
+            if (e != cudaSuccess) return (int)e;                                                                              \
+        }                                                                                                                     \
+        code = launch_pdl(gk, dim3(ns, H), dim3(ML_GTHREADS), gsmem, s, (const AT*)qkv, ld, oq, ok, z, bi, bf, cap, qscale, segs, \
+                          row_slot, state, (size_t)state_stride, fac, H, dk, dv, vec);                                        \
+        if (code) return code;                                                                                                \
+        code = launch_pdl(sk, grid, dim3(ML_COLT + ML_PROD), smem, s, (const AT*)qkv, ld, oq, ok, ov, (const float*)fac, qscale, \
+                          segs, row_slot, state, (size_t)state_stride, raw, H, dk, dv, kp, vec);                               \
+        if (code) return code;                                                                                                \
+    } while (0)
     int code;
     if (ns > 0) {
-        if (is_bf16) {
-            code = launch_pdl(mlstm_gates_kernel<bf16>, dim3(ns, H), dim3(ML_GTHREADS), gsmem, s, (const bf16*)qkv, ld, oq, ok, z,
-                              bi, bf, cap, qscale, segs, row_slot, state, (size_t)state_stride, fac, H, dk, dv, vec);
-            if (code) return code;
-            code = launch_pdl(mlstm_scan_kernel<bf16>, grid, dim3(ML_COLT + ML_PROD), smem, s, (const bf16*)qkv, ld, oq, ok, ov, fac,
-                              qscale, segs, row_slot, state, (size_t)state_stride, raw, H, dk, dv, kp, vec);
-        } else {
-            code = launch_pdl(mlstm_gates_kernel<float>, dim3(ns, H), dim3(ML_GTHREADS), gsmem, s, (const float*)qkv, ld, oq, ok,
-                              z, bi, bf, cap, qscale, segs, row_slot, state, (size_t)state_stride, fac, H, dk, dv, vec);
-            if (code) return code;
-            code = launch_pdl(mlstm_scan_kernel<float>, grid, dim3(ML_COLT + ML_PROD), smem, s, (const float*)qkv, ld, oq, ok, ov, fac,
-                              qscale, segs, row_slot, state, (size_t)state_stride, raw, H, dk, dv, kp, vec);
-        }
-        if (code) return code;
+        if (is_bf16) ML_LAUNCH(bf16);
+        else ML_LAUNCH(float);
     }
+#undef ML_LAUNCH
     if (is_bf16)
         return launch_pdl(mlstm_finish_kernel<bf16>, dim3(T), dim3(256), 0, s, raw, (const bf16*)qkv, ld, og, wnorm, (bf16*)out,
                           row_slot, H, dv, eps, mult);
