@@ -32,7 +32,7 @@ template <int RANK>
 __global__ void __launch_bounds__(128) latent_attention_mma_kernel(
     const float* q_lat, const bf16* q, int ldq, int q_off, bf16* out, float* part_o, float* part_ml, const int* positions,
     const int* row_slot, const bf16* pages, const int* __restrict__ table, int max_blocks, int bs, int n_heads, int rot,
-    const float* __restrict__ freq, float mag, int dims, float scale, int n_splits, int split_keys) {
+    const float* __restrict__ freq, float mag, int dims, float scale, int n_splits, int split_keys, int bs_shift) {
     extern __shared__ __align__(16) unsigned char lm_smem[];
     const int D = RANK + rot, LDK = D + 8;
     bf16* Qs = reinterpret_cast<bf16*>(lm_smem);                       // [16][LDK]
@@ -91,9 +91,12 @@ __global__ void __launch_bounds__(128) latent_attention_mma_kernel(
             bf16* dst = Ks + st * LM_KEYS * LDK;
             for (int j = warp; j < LM_KEYS; j += 4) {
                 const int key = base + j;
+                // page and place in the page: shifts when the page size is a power of two (bs_shift >= 0)
+                const int blk_i = bs_shift >= 0 ? key >> bs_shift : key / bs;
+                const int in_page = bs_shift >= 0 ? key & (bs - 1) : key - blk_i * bs;
                 int page = -1;
-                if (key < k_end) page = trow[key / bs];
-                const bf16* src = pages + ((size_t)(page >= 0 ? page : 0) * bs + (key % bs)) * D;
+                if (key < k_end) page = trow[blk_i];
+                const bf16* src = pages + ((size_t)(page >= 0 ? page : 0) * bs + in_page) * D;
                 for (int c = lane; c < chunks; c += 32) {
                     if (page >= 0) lm_cp_async16(dst + j * LDK + c * 8, src + c * 8);
                     else *reinterpret_cast<uint4*>(dst + j * LDK + c * 8) = make_uint4(0u, 0u, 0u, 0u);   // no key: zeros, never garbage
@@ -103,6 +106,9 @@ __global__ void __launch_bounds__(128) latent_attention_mma_kernel(
         const int n_blocks = (k_end - k_begin + LM_KEYS - 1) / LM_KEYS;
         load_block(0, k_begin);
         lm_commit();
+        // scores are kept in units of log2 (scale * log2 e), so that the exponentials are one ex2 each, as in the
+        // framework's other tensor-core attention kernels; the maxima of the splits are in the same units
+        const float scale2 = scale * 1.4426950408889634f;
         const int ksteps = D / 16, ks_half = (ksteps + 1) / 2;
         const int kh = warp & 1, part = warp >> 1;
         const int ks0 = part * ks_half, ks1 = min(ksteps, ks0 + ks_half);
@@ -142,7 +148,7 @@ __global__ void __launch_bounds__(128) latent_attention_mma_kernel(
                 for (int e = 0; e < 8; ++e) {
                     const int key = (e >> 2) * 16 + ((e >> 1) & 1) * 8 + 2 * qd + (e & 1);
                     const int row = r0 + rr * 8;
-                    const float v = (Ss[row * SP + key] + Ss[LM_HEADS * SP + row * SP + key]) * scale;
+                    const float v = (Ss[row * SP + key] + Ss[LM_HEADS * SP + row * SP + key]) * scale2;
                     p[rr][e] = key < n_valid ? v : -INFINITY;
                     mx[rr] = fmaxf(mx[rr], p[rr][e]);
                 }
@@ -152,11 +158,11 @@ __global__ void __launch_bounds__(128) latent_attention_mma_kernel(
                 mx[rr] = fmaxf(mx[rr], __shfl_xor_sync(0xffffffffu, mx[rr], 1));
                 mx[rr] = fmaxf(mx[rr], __shfl_xor_sync(0xffffffffu, mx[rr], 2));
                 const float m_new = fmaxf(m_run[rr], mx[rr]);
-                const float corr = m_run[rr] == -INFINITY ? 0.f : expf(m_run[rr] - m_new);
+                const float corr = ex2_approx(m_run[rr] - m_new);          // 2^(-inf) = 0 at the first block
                 float sum = 0.f;
 #pragma unroll
                 for (int e = 0; e < 8; ++e) {
-                    p[rr][e] = p[rr][e] == -INFINITY ? 0.f : expf(p[rr][e] - m_new);
+                    p[rr][e] = ex2_approx(p[rr][e] - m_new);               // a masked key: 2^(-inf) = 0
                     sum += p[rr][e];
                 }
                 sum += __shfl_xor_sync(0xffffffffu, sum, 1);
@@ -209,7 +215,7 @@ __global__ void __launch_bounds__(128) latent_attention_mma_kernel(
     }
 }
 
-// out[t, h] = sum_s w_s O_s / sum_s w_s l_s with w_s = exp(m_s - max m), splits in order.
+// out[t, h] = sum_s w_s O_s / sum_s w_s l_s with w_s = 2^(m_s - max m) (the maxima are in units of log2), splits in order.
 template <int RANK>
 __global__ void __launch_bounds__(128) latent_merge_kernel(const float* part_o, const float* part_ml, bf16* out, int n_splits) {
     pdl_trigger();
@@ -219,12 +225,12 @@ __global__ void __launch_bounds__(128) latent_merge_kernel(const float* part_o, 
     float M = -INFINITY;
     for (int s = 0; s < n_splits; ++s) M = fmaxf(M, ml[2 * s]);
     float den = 0.f;
-    for (int s = 0; s < n_splits; ++s) den += ml[2 * s] == -INFINITY ? 0.f : expf(ml[2 * s] - M) * ml[2 * s + 1];
+    for (int s = 0; s < n_splits; ++s) den += ml[2 * s] == -INFINITY ? 0.f : exp2f(ml[2 * s] - M) * ml[2 * s + 1];
     const float inv = den > 0.f ? 1.f / den : 0.f;
     for (int d = threadIdx.x; d < RANK; d += 128) {
         float acc = 0.f;
         for (int s = 0; s < n_splits; ++s)
-            if (ml[2 * s] != -INFINITY) acc = fmaf(expf(ml[2 * s] - M), part_o[(th * n_splits + s) * RANK + d], acc);
+            if (ml[2 * s] != -INFINITY) acc = fmaf(exp2f(ml[2 * s] - M), part_o[(th * n_splits + s) * RANK + d], acc);
         out[th * RANK + d] = __float2bfloat16_rn(acc * inv);
     }
 }
@@ -243,9 +249,11 @@ static int launch_latent_mma(const float* q_lat, const void* q, int ldq, int q_o
         if (e != cudaSuccess) return (int)e;
         raised = true;
     }
+    int bs_shift = -1;
+    if (bs > 0 && (bs & (bs - 1)) == 0) { bs_shift = 0; while ((1 << bs_shift) < bs) ++bs_shift; }
     int code = launch_pdl(latent_attention_mma_kernel<RANK>, dim3(T, (n_heads + LM_HEADS - 1) / LM_HEADS, n_splits), dim3(128), smem, s,
                           q_lat, (const bf16*)q, ldq, q_off, (bf16*)out, part_o, part_ml, positions, row_slot, (const bf16*)pages,
-                          table, max_blocks, bs, n_heads, rot, freq, mag, dims, scale, n_splits, split_keys);
+                          table, max_blocks, bs, n_heads, rot, freq, mag, dims, scale, n_splits, split_keys, bs_shift);
     if (code || n_splits == 1) return code;
     return launch_pdl(latent_merge_kernel<RANK>, dim3(T * n_heads), dim3(128), 0, s, (const float*)part_o, (const float*)part_ml,
                       (bf16*)out, n_splits);
