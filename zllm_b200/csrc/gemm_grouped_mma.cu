@@ -6,7 +6,7 @@
 //   first product  (swiglu): 64 gate rows and the 64 up rows of the same outputs; the rows of x are
 //                  gathered (x[perm[i] / top]); act[i][n] = silu(gate) * up in bfloat16;
 //   second product:          128 rows of the down matrix; y[perm[i]][n] in float32 (scattered).
-// K runs in pieces of 32 or 64 through a cp.async ring of three or four stages; fragments come from shared memory with
+// K runs in pieces of 64 or 32 through a three-stage cp.async ring; fragments come from shared memory with
 // ldmatrix and go to mma.sync m16n8k16; eight warps as 4 x 2, each 32 rows x 64 columns.  Every
 // output is the sum over k in a fixed order that depends on K alone, so a row's result does not
 // depend on which other rows share its tile.  Needs K % 32 == 0 and 16-byte aligned operands;
@@ -15,9 +15,8 @@
 
 #define TM 128
 #define TN 128
-// K is walked in pieces of TK = 32 through 3 stages (61 KB of shared memory, three CTAs per SM: many rows,
-// bound by the tensor cores) or of TK = 64 through 3 stages (110 KB, two CTAs per SM with 72 KB of weights
-// in flight: few rows, bound by the stream of weights).  A shared-memory row holds TK + 8 bfloat16, so that
+// K is walked in pieces of TK = 64 through 3 stages (110 KB of shared memory, two CTAs per SM, 72 KB of weights
+// in flight per SM) when K is a multiple of 64, else in pieces of 32 (61 KB, three CTAs per SM).  A shared-memory row holds TK + 8 bfloat16, so that
 // the eight rows of an ldmatrix fall on distinct banks.
 
 __device__ __forceinline__ void cp_async16(void* dst, const void* src) {
@@ -194,7 +193,9 @@ ZLLM_API int zllm_gemm_experts_mma(const void* x, const void* w, const void* wu,
     if (n_pairs <= 0 || N <= 0) return 0;
     if (K <= 0 || (K % 32) || E <= 0 || top <= 0 || (((uintptr_t)x | (uintptr_t)w | (uintptr_t)wu) & 15)) return ZLLM_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
-    const bool few = n_pairs <= 256 && K % 64 == 0;          // few rows: the deeper ring of wider pieces
+    // pieces of 64 wherever K allows: measured at 2,048 rows of 32 experts 0.44 against 0.50 ms per layer, and at few
+    // rows the wider pieces keep more weights in flight
+    const bool few = K % 64 == 0;
     const size_t smem = few ? (size_t)3 * (TM + TN) * 72 * sizeof(bf16) : (size_t)3 * (TM + TN) * 40 * sizeof(bf16);
     static bool raised = false;
     if (!raised) {
@@ -279,7 +280,7 @@ ZLLM_API int zllm_gemm_heads_mma(const void* x, int ldx, int xg, const void* w, 
     if (T <= 0 || N <= 0 || G <= 0) return 0;
     if (K <= 0 || (K % 32) || (ldx % 8) || (xg % 8) || (((uintptr_t)x | (uintptr_t)w) & 15)) return ZLLM_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
-    const bool few = T <= 256 && K % 64 == 0;
+    const bool few = K % 64 == 0;
     const size_t smem = few ? (size_t)3 * (TM + TN) * 72 * sizeof(bf16) : (size_t)3 * (TM + TN) * 40 * sizeof(bf16);
     static bool raised = false;
     if (!raised) {
