@@ -1,7 +1,7 @@
 """Small Sepirax configurations of the test-suite, model folders with random weights, and
 helpers that read such a folder for the plain implementation.
 
-The two configurations differ in every size and option: layer order (which mixer comes first, a
+The first two configurations differ in every size and option: layer order (which mixer comes first, a
 mixer twice in a row), head counts (also odd ones), head sizes that differ from value sizes, a
 rotated part whose first half only is rotated, YaRN scaling or none, expert counts and groups
 (also no groups and a single choice), a layer without a feed-forward, the residual factor, the
@@ -48,8 +48,22 @@ SEP_B = {
         {"type": "latent_attention", "mlp": _moe(24, 6, 3, 3, 2), "mixer": _latent(5, 8, 16, 16, 40, 32, 40, None)},
     ],
 }
+# Sizes that the tensor-core kernels take (a latent of 64 with a rotated part of 16, inner sizes that are
+# multiples of 32 and 64, a memory whose rows fill the registers exactly), so that those kernels also run
+# inside the whole-model tests in bfloat16
+SEP_C = {
+    "architecture": "Sepirax", "vocab": 264, "width": 128, "norm": {"eps": 1e-6}, "residual_mult": 0.8,
+    "embedding": {"scale": 2.0}, "logit_softcap": 25.0,
+    "layers": [
+        {"type": "latent_attention", "mlp": _moe(64, 8, 2, 2, 1),
+         "mixer": _latent(4, 32, 16, 16, 32, 64, 64, {"factor": 4.0, "original": 32, "fast": 8.0, "slow": 1.0})},
+        {"type": "mlstm", "mlp": _moe(64, 8, 2, 2, 1), "mixer": {"heads": 2, "dim": 32, "vdim": 64, "gate_cap": 12.0}},
+        {"type": "latent_attention", "mlp": None,
+         "mixer": _latent(4, 32, 16, 16, 32, 64, 64, {"factor": 4.0, "original": 32, "fast": 8.0, "slow": 1.0})},
+    ],
+}
 # name -> (configuration, page size, weight seed, std of matrices)
-SEPIRAX = {"A": (SEP_A, 16, 11, 0.08), "B": (SEP_B, 8, 12, 0.1)}
+SEPIRAX = {"A": (SEP_A, 16, 11, 0.08), "B": (SEP_B, 8, 12, 0.1), "C": (SEP_C, 16, 13, 0.08)}
 
 
 def make_sepirax_dir(tmp_path, name, dtype="float32", std=None, edit=None):

@@ -16,9 +16,10 @@ from sepirax_util import SEPIRAX, make_sepirax_dir, read_dir
 
 pytestmark = pytest.mark.gpu
 
-# bound of the bfloat16 comparisons, as a fraction of the largest |logit|: twice the worst observed on a
-# B200 over these tests (model A 0.0042, model B 0.0076)
-BF16_OF_SCALE = 0.016
+# bounds of the bfloat16 comparisons, as a fraction of the request's largest |logit|, per test model: twice the
+# worst observed on a B200 over these tests (A 0.0042, B 0.0076, C 0.0170: C's logits are small, 0.8 at most, so
+# the same rounding is a larger fraction; with the tensor-core kernels switched off C reads 0.0164)
+BF16_OF_SCALE = {"A": 0.0085, "B": 0.016, "C": 0.034}
 
 
 @pytest.fixture(scope="module")
@@ -261,7 +262,7 @@ def _runner(d, name, dtype, num_blocks, max_rows=512, slots=4, graphs=False):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
 def test_every_way_of_cutting_agrees_with_plain(tmp_path, name, dtype):
     d = make_sepirax_dir(tmp_path, name, dtype)
     cfg, w = read_dir(d)
@@ -280,7 +281,7 @@ def test_every_way_of_cutting_agrees_with_plain(tmp_path, name, dtype):
         if dtype == "float32":
             TR.compare(got, ref, reqs, prefix, 3e-4, 0.0, f"sepirax {name} {prefix} float32")
         else:
-            TR.compare(got, ref, reqs, prefix, 0.0, BF16_OF_SCALE, f"sepirax {name} {prefix} bfloat16")
+            TR.compare(got, ref, reqs, prefix, 0.0, BF16_OF_SCALE[name], f"sepirax {name} {prefix} bfloat16")
     if dtype == "float32":
         # the order of every sum is fixed by the position: the ways of cutting agree bit for bit
         for rid, toks in reqs:
@@ -302,7 +303,7 @@ def test_long_decoding_in_float32(tmp_path):
 
 @pytest.mark.parametrize("graphs", [False, True])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
 def test_greedy_generation_through_the_engine(tmp_path, name, dtype, graphs):
     from zllm_b200 import Engine, SamplingParams
     d = make_sepirax_dir(tmp_path, name, dtype, std=0.2)
