@@ -62,8 +62,19 @@ SEP_C = {
          "mixer": _latent(4, 32, 16, 16, 32, 64, 64, {"factor": 4.0, "original": 32, "fast": 8.0, "slow": 1.0})},
     ],
 }
+# Sizes that are multiples of nothing: no vector load, no tensor-core tile and no 16-byte boundary fits, so every
+# kernel's general path runs (a width of 76, a cache row of 42 numbers, 9 experts in 3 groups, 5 heads of 12 x 18)
+SEP_D = {
+    "architecture": "Sepirax", "vocab": 101, "width": 76, "norm": {"eps": 1e-5}, "residual_mult": 0.9,
+    "embedding": {"scale": 3.0}, "logit_softcap": 15.0,
+    "layers": [
+        {"type": "mlstm", "mlp": _moe(22, 9, 4, 3, 2), "mixer": {"heads": 5, "dim": 12, "vdim": 18, "gate_cap": 9.0}},
+        {"type": "latent_attention", "mlp": _moe(22, 9, 4, 3, 2),
+         "mixer": _latent(3, 10, 6, 4, 14, 20, 36, {"factor": 2.0, "original": 16, "fast": 4.0, "slow": 0.5})},
+    ],
+}
 # name -> (configuration, page size, weight seed, std of matrices)
-SEPIRAX = {"A": (SEP_A, 16, 11, 0.08), "B": (SEP_B, 8, 12, 0.1), "C": (SEP_C, 16, 13, 0.08)}
+SEPIRAX = {"A": (SEP_A, 16, 11, 0.08), "B": (SEP_B, 8, 12, 0.1), "C": (SEP_C, 16, 13, 0.08), "D": (SEP_D, 16, 16, 0.15)}
 
 
 def make_sepirax_dir(tmp_path, name, dtype="float32", std=None, edit=None):

@@ -18,8 +18,10 @@ pytestmark = pytest.mark.gpu
 
 # bounds of the bfloat16 comparisons, as a fraction of the request's largest |logit|, per test model: twice the
 # worst observed on a B200 over these tests (A 0.0042, B 0.0076, C 0.0170: C's logits are small, 0.8 at most, so
-# the same rounding is a larger fraction; with the tensor-core kernels switched off C reads 0.0164)
-BF16_OF_SCALE = {"A": 0.0085, "B": 0.016, "C": 0.034}
+# the same rounding is a larger fraction; with the tensor-core kernels switched off C reads 0.0164; D 0.0257: it
+# chooses 4 of 9 experts, and where two router scores are closer than the rounding of the activations the
+# bfloat16 engine may choose the other one -- median 0.0024, 99 % of the positions under 0.011)
+BF16_OF_SCALE = {"A": 0.0085, "B": 0.016, "C": 0.034, "D": 0.052}
 
 
 @pytest.fixture(scope="module")
@@ -262,7 +264,7 @@ def _runner(d, name, dtype, num_blocks, max_rows=512, slots=4, graphs=False):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_every_way_of_cutting_agrees_with_plain(tmp_path, name, dtype):
     d = make_sepirax_dir(tmp_path, name, dtype)
     cfg, w = read_dir(d)
