@@ -218,19 +218,30 @@ __global__ void __launch_bounds__(128) latent_attention_mma_kernel(
 // out[t, h] = sum_s w_s O_s / sum_s w_s l_s with w_s = 2^(m_s - max m) (the maxima are in units of log2), splits in order.
 template <int RANK>
 __global__ void __launch_bounds__(128) latent_merge_kernel(const float* part_o, const float* part_ml, bf16* out, int n_splits) {
+    __shared__ float wgt[64];                            // a split's weight, once for all columns (n_splits <= 64)
+    __shared__ float inv_s;
     pdl_trigger();
     pdl_wait();
     const size_t th = blockIdx.x;                        // (row, head)
     const float* ml = part_ml + th * n_splits * 2;
-    float M = -INFINITY;
-    for (int s = 0; s < n_splits; ++s) M = fmaxf(M, ml[2 * s]);
-    float den = 0.f;
-    for (int s = 0; s < n_splits; ++s) den += ml[2 * s] == -INFINITY ? 0.f : exp2f(ml[2 * s] - M) * ml[2 * s + 1];
-    const float inv = den > 0.f ? 1.f / den : 0.f;
+    if (threadIdx.x < 32) {
+        float M = -INFINITY;
+        for (int s = threadIdx.x; s < n_splits; s += 32) M = fmaxf(M, ml[2 * s]);
+        M = warp_max(M);
+        float den = 0.f;
+        for (int s = threadIdx.x; s < n_splits; s += 32) {
+            const float w = ml[2 * s] == -INFINITY ? 0.f : exp2f(ml[2 * s] - M);
+            wgt[s] = w;
+            den += w * ml[2 * s + 1];
+        }
+        den = warp_sum(den);
+        if (threadIdx.x == 0) inv_s = den > 0.f ? 1.f / den : 0.f;
+    }
+    __syncthreads();
+    const float inv = inv_s;
     for (int d = threadIdx.x; d < RANK; d += 128) {
         float acc = 0.f;
-        for (int s = 0; s < n_splits; ++s)
-            if (ml[2 * s] != -INFINITY) acc = fmaf(exp2f(ml[2 * s] - M), part_o[(th * n_splits + s) * RANK + d], acc);
+        for (int s = 0; s < n_splits; ++s) acc = fmaf(wgt[s], part_o[(th * n_splits + s) * RANK + d], acc);
         out[th * RANK + d] = __float2bfloat16_rn(acc * inv);
     }
 }
@@ -268,7 +279,7 @@ ZLLM_API int zllm_latent_attention_mma(const float* q_lat, const void* q, int ld
                                        const float* freq, float mag, int dims, float scale, int n_splits, int split_keys,
                                        void* stream) {
     if (T <= 0) return 0;
-    if (dims > rot || (dims & 1) || dims > 2 * LM_MAXHALF || (rot % 16) || n_heads <= 0 || rot > q_off || n_splits < 1 || (n_splits > 1 && split_keys % LM_KEYS) ||
+    if (dims > rot || (dims & 1) || dims > 2 * LM_MAXHALF || (rot % 16) || n_heads <= 0 || rot > q_off || n_splits < 1 || n_splits > 64 || (n_splits > 1 && split_keys % LM_KEYS) ||
         (((uintptr_t)pages | (uintptr_t)out | (uintptr_t)part_o) & 15))
         return ZLLM_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;

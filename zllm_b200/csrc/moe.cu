@@ -39,7 +39,8 @@ __global__ void __launch_bounds__(256) moe_route_kernel(const AT* h, const AT* _
         const AT* w = wr + (size_t)e * H;
         float dot = 0.f;
         if (vec) {                                   // pieces of eight values, a lane's pieces 256 apart
-            for (int i = lane * 8; i < H; i += 256) {
+#pragma unroll 4
+            for (int i = lane * 8; i < H; i += 256) {       // unrolled: several pairs of loads in flight
                 float a[8], b[8];
                 moe_load8(hr + i, a);
                 moe_load8(w + i, b);
