@@ -26,8 +26,10 @@
 #include <math.h>
 
 #define ML_NL 16          // n entries per lane: dk <= 512
-#define ML_CHUNK 8        // tokens staged at a time by the scan
-#define ML_COLT 128
+#define ML_CHUNK 8        // tokens staged at a time
+#define ML_COLT 256       // threads of a scan block that walk columns of S
+#define ML_RPT 16         // rows of S per thread
+#define ML_PROD 64        // threads of a scan block that only bring in the next chunk
 
 __device__ __forceinline__ bool segment_of(const int* segs, const int* row_slot, int s, int& row0, int& rows, int& slot) {
     if (segs != nullptr) {
@@ -39,7 +41,6 @@ __device__ __forceinline__ bool segment_of(const int* segs, const int* row_slot,
 }
 
 #define ML_GTHREADS 128   // threads of a gates block: all stage a chunk, the first warp walks it
-#define ML_MAXDK (32 * ML_NL)
 
 // eight consecutive operand values as float32 (the address is 16-byte aligned for bfloat16, 32 for float32)
 __device__ __forceinline__ void load8(const bf16* p, float (&v)[8]) {
@@ -98,8 +99,8 @@ __global__ void __launch_bounds__(ML_GTHREADS) mlstm_gates_kernel(
     const AT* qkv, int ld, int oq, int ok, const float* z, const float* __restrict__ bi, const float* __restrict__ bf,
     float cap, float qscale, const int* __restrict__ segs, const int* row_slot, float* state, size_t state_stride,
     float* fac, int H, int dk, int dv, int vec) {
-    // A chunk of eight tokens at a time: all threads stage q, k and the two log gates; then the first warp
-    // walks the chunk: the running maximum by one lane (a chain of a few operations per token), the
+    // A chunk of eight tokens at a time: three warps stage q, k and the two log gates of the NEXT chunk while
+    // the first warp walks this one: the running maximum as a short chain (a few operations per token), the
     // exponentials of the chunk by eight lanes at once, n and the partial n.q token by token, and the
     // eight sums over the lanes together at the end, so that few long latencies follow one another.
     extern __shared__ float qk_stage[];                      // [2][ML_CHUNK][2 * dk]: the chunk walked and the next one
@@ -198,11 +199,6 @@ __global__ void __launch_bounds__(ML_GTHREADS) mlstm_gates_kernel(
     if (lane == 0) np[dk] = m;
 }
 
-#undef ML_COLT
-#define ML_COLT 256       // threads of a scan block
-#define ML_RPT 16         // rows of S per thread
-
-#define ML_PROD 64        // threads of a scan block that only bring in the next chunk
 
 // KPT > 0: kp is KPT and dk exactly KPT * ML_RPT (offsets known to the compiler, no bounds checks); 0: any.
 template <typename AT, int KPT>
