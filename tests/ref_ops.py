@@ -152,9 +152,12 @@ class RefOps:
         out.copy_(torch.where(live, y, torch.zeros_like(y)).to(out.dtype))
 
     # ---- mixture of experts ----------------------------------------------------------------------
-    def moe_route(self, h, w_router, top, groups, keep, idx, weights):
-        s = torch.softmax(h.float() @ w_router.float().T, dim=-1)
-        T, E = s.shape
+    def moe_route(self, h, w_router, top, groups, keep, idx, weights, score="softmax", normalise=True, n_shared=0,
+                  shared_gate=False):
+        z = h.float() @ w_router.float().T
+        E = z.shape[1] - (1 if shared_gate else 0)
+        s = torch.softmax(z[:, :E], dim=-1) if score == "softmax" else torch.sigmoid(z[:, :E])
+        T = s.shape[0]
         per = E // groups
         gbest = s.reshape(T, groups, per).max(-1).values
         kept = torch.zeros(T, groups, dtype=torch.bool)
@@ -162,19 +165,113 @@ class RefOps:
         masked = torch.where(kept[:, :, None].expand(T, groups, per).reshape(T, E), s, torch.full_like(s, -1.0))
         ch = torch.topk(masked, top, dim=-1).indices
         sc = torch.gather(s, 1, ch)
-        idx.copy_(ch.to(idx.dtype))
-        weights.copy_(sc / (sc.sum(-1, keepdim=True) + 1e-20))
+        idx[:, :top] = ch.to(idx.dtype)
+        weights[:, :top] = sc / (sc.sum(-1, keepdim=True) + 1e-20) if normalise else sc
+        for c in range(n_shared):
+            idx[:, top + c] = E + c
+            weights[:, top + c] = torch.sigmoid(z[:, E]) if shared_gate else 1.0
 
-    def moe_experts(self, h, idx, weights, w_gate, w_up, w_down, residual, scale, ws):
+    @staticmethod
+    def _expert_act(a, activation):
+        if activation == "gelu":
+            return 0.5 * a * (1.0 + torch.erf(a / math.sqrt(2.0)))
+        if activation == "gelu_tanh":
+            return 0.5 * a * (1.0 + torch.tanh(math.sqrt(2.0 / math.pi) * (a + 0.044715 * a ** 3)))
+        return a / (1.0 + torch.exp(-a))
+
+    def moe_experts(self, h, idx, weights, w_gate, w_up, w_down, residual, scale, ws, n_input_weighted=0, activation="silu",
+                    accumulate=True):
         x = h.float()
         for t in range(x.shape[0]):
             acc = torch.zeros(x.shape[1])
             for j in range(idx.shape[1]):
                 e = int(idx[t, j])
-                a = x[t] @ w_gate[e].float().T
-                act = (a / (1.0 + torch.exp(-a)) * (x[t] @ w_up[e].float().T)).to(h.dtype).float()
-                acc = acc + weights[t, j] * (act @ w_down[e].float().T)
-            residual[t] += scale * acc
+                on_input = j < n_input_weighted
+                c = float(weights[t, j]) if on_input else 1.0
+                up = (x[t] @ w_up[e].float().T) * c
+                if w_gate is not None:
+                    a = (x[t] @ w_gate[e].float().T) * c
+                    act = a / (1.0 + torch.exp(-a)) * up
+                else:
+                    act = self._expert_act(up, activation)
+                act = act.to(h.dtype).float()
+                acc = acc + (1.0 if on_input else weights[t, j]) * (act @ w_down[e].float().T)
+            if accumulate:
+                residual[t] += scale * acc
+            else:
+                residual[t] = scale * acc
+
+    # ---- a branch's output norm, biases ----------------------------------------------------------
+    def rmsnorm_add(self, y, bias, weight, eps, residual):
+        v = y.float() if bias is None else y.float() + bias.float()
+        residual.add_(v * torch.rsqrt((v * v).mean(dim=-1, keepdim=True) + eps) * weight.float())
+
+    def add_bias(self, x, bias):
+        x.add_(bias.float())
+
+    def bias_silu_mul(self, gu, bias, out):
+        I = out.shape[1]
+        g = gu[:, :I].float() + bias[:I].float()
+        u = gu[:, I:2 * I].float() + bias[I:].float()
+        out.copy_((g / (1.0 + torch.exp(-g)) * u).to(out.dtype))
+
+    # ---- attention with a window that keeps the first positions ------------------------------------
+    def rotate_store_kv(self, proj, off_k, off_v, ctx, freqs, cache, nq, nkv, dk, dv, write_cache=True):
+        T = proj.shape[0]
+        pos = ctx.positions.long()
+        x = proj.float()
+        if freqs is not None and freqs.dims:
+            half = freqs.dims // 2
+            ang = pos.float()[:, None] * freqs.freq.float()[None, :]            # float32 angles
+            c, s = (torch.cos(ang) * freqs.magnitude)[:, None, :], (torch.sin(ang) * freqs.magnitude)[:, None, :]
+            for start, n in ((0, nq), (off_k, nkv)):
+                hd = x[:, start:start + n * dk].reshape(T, n, dk).clone()
+                if freqs.interleaved:
+                    a, b = hd[..., 0:freqs.dims:2].clone(), hd[..., 1:freqs.dims:2].clone()
+                    hd[..., 0:freqs.dims:2] = a * c - b * s
+                    hd[..., 1:freqs.dims:2] = b * c + a * s
+                else:
+                    a, b = hd[..., :half].clone(), hd[..., half:freqs.dims].clone()
+                    hd[..., :half] = a * c - b * s
+                    hd[..., half:freqs.dims] = b * c + a * s
+                x[:, start:start + n * dk] = hd.reshape(T, n * dk)
+        live = (ctx.row_slot[:T] >= 0)[:, None]
+        proj.copy_(torch.where(live, x, proj.float()).to(proj.dtype))
+        if not write_cache:
+            return
+        bs = cache.block_size
+        for t in range(T):
+            slot = int(ctx.row_slot[t])
+            if slot < 0:
+                continue
+            p = int(pos[t])
+            page = int(cache.block_table[slot, p // bs])
+            assert page >= 0, "write to a position without a page"
+            cache.k_pages[page, :, p % bs, :] = proj[t, off_k:off_k + nkv * dk].reshape(nkv, dk).to(cache.k_pages.dtype)
+            cache.v_pages[page, :, p % bs, :] = proj[t, off_v:off_v + nkv * dv].reshape(nkv, dv).to(cache.v_pages.dtype)
+
+    def window_attention(self, proj, off_g, out, ctx, cache, nq, nkv, dk, dv, scale, window, keep_first):
+        T = proj.shape[0]
+        bs = cache.block_size
+        rep = nq // nkv
+        for t in range(T):
+            slot = int(ctx.row_slot[t])
+            if slot < 0:
+                out[t].zero_()
+                continue
+            p = int(ctx.positions[t])
+            q = proj[t, :nq * dk].float().reshape(nq, dk)
+            lo = 0 if not window else max(0, p - window + 1)
+            idx = torch.tensor([j for j in range(p + 1) if j >= lo or j < (keep_first or 0)])
+            pages = cache.block_table[slot, (idx // bs).long()].long()
+            assert (pages >= 0).all(), "read of a position whose page was given back"
+            K = cache.k_pages[pages, :, (idx % bs).long(), :].float().repeat_interleave(rep, dim=1)    # [n, nq, dk]
+            V = cache.v_pages[pages, :, (idx % bs).long(), :].float().repeat_interleave(rep, dim=1)
+            pr = torch.softmax(torch.einsum("hd,nhd->hn", q, K) * scale, dim=-1)
+            o = torch.einsum("hn,nhd->hd", pr, V)
+            if off_g >= 0:
+                o = o * torch.sigmoid(proj[t, off_g:off_g + nq].float())[:, None]
+            out[t].copy_(o.reshape(-1).to(out.dtype))
 
     # ---- BNORM (shaders.rs:545-564) --------------------------------------------------
     def rmsnorm(self, x, weight, eps, out, rows=None):

@@ -13,10 +13,12 @@ request slots are a stack, slot 0 first, kept for the request's life
 (src/backend/gpu/batch.rs:65-66).
 
 Beyond the reference (whose layers all have identical pools): layers are put
-into *groups* by what they need -- (kv heads, head size, window, value rows or not) -- and each
+into *groups* by what they need -- (kv heads, head size, window, value rows or not, their size,
+kept first positions) -- and each
 group has its own pool and tables under the shared slot id.  A group with a
 window gives pages back during the request, as soon as every position of the
-page has fallen out of the window of the next query.  Per-request state of
+page has fallen out of the window of the next query; the pages of the first
+``keep_first`` positions stay until the request ends.  Per-request state of
 fixed size lives in arrays [slots, ...] indexed by the slot id, zeroed at
 admission.
 
@@ -116,7 +118,7 @@ class KVLayerView:
     """What a mixer sees of its cache: key pages, value pages, the group's table."""
 
     k_pages: torch.Tensor        # [num_pages, n_kv_heads, block_size, head_dim]
-    v_pages: Optional[torch.Tensor]     # None for a cache spec without value rows
+    v_pages: Optional[torch.Tensor]     # [.., value_dim or head_dim]; None for a cache spec without value rows
     block_table: torch.Tensor    # [max_slots, max_blocks] int32, NO_PAGE where none
     block_size: int
     window: Optional[int]
@@ -137,13 +139,16 @@ class KVGroup:
         self.spec = spec
         self.block_size = block_size
         self.window = spec.window
+        # blocks that hold one of the first ``keep_first`` positions: a window never gives them back
+        self.keep_blocks = -(-int(spec.keep_first) // block_size) if spec.window is not None else 0
         self.max_blocks = -(-max_len // block_size)
         self.pool = PagePool(num_pages)
         self.entries: List[int] = []                   # run entries whose cache lives here
         self.table = np.full((max_slots, self.max_blocks), NO_PAGE, dtype=np.int32)
         self.n_blocks = [0] * max_slots                # logical blocks ever reached (high-water)
-        self.first_live = [0] * max_slots              # lowest logical block not yet given back
+        self.first_live = [0] * max_slots              # lowest logical block not yet given back (kept first blocks aside)
         self.storage: Optional[torch.Tensor] = None    # [entries, 2, pages, kv heads, block, head_dim]
+        self.value_storage: Optional[torch.Tensor] = None   # [entries, pages, kv heads, block, value_dim] when the sizes differ
         self.table_dev: Optional[torch.Tensor] = None
         self.dirty: set = set()
 
@@ -185,7 +190,8 @@ class CacheManager:
             if cache_of is not None or spec is None:
                 continue
             if isinstance(spec, KVCacheSpec):
-                key = (spec.n_kv_heads, spec.head_dim, spec.window, spec.values)
+                key = (spec.n_kv_heads, spec.head_dim, spec.window, spec.values, spec.value_dim,
+                       spec.keep_first if spec.window is not None else 0)
                 g = by_key.get(key)
                 if g is None:
                     g = KVGroup(len(self.groups), spec, self.block_size, num_pages, max_slots, max_len)
@@ -216,17 +222,21 @@ class CacheManager:
         dev = self.device
         for g in self.groups:
             s = g.spec
-            g.storage = torch.zeros((len(g.entries), 2 if s.values else 1, g.pool.num_pages, s.n_kv_heads, self.block_size,
-                                     s.head_dim),
+            own_values = s.values and s.value_dim is not None and s.value_dim != s.head_dim
+            g.storage = torch.zeros((len(g.entries), 2 if s.values and not own_values else 1, g.pool.num_pages, s.n_kv_heads,
+                                     self.block_size, s.head_dim),
                                     dtype=self.dtype, device=dev)
+            if own_values:
+                g.value_storage = torch.zeros((len(g.entries), g.pool.num_pages, s.n_kv_heads, self.block_size, s.value_dim),
+                                              dtype=self.dtype, device=dev)
             g.table_dev = torch.full((self.max_slots, g.max_blocks), NO_PAGE, dtype=torch.int32, device=dev)
             g.table_pinned = torch.from_numpy(g.table)
             if dev.type == "cuda":
                 g.table_pinned = torch.full((self.max_slots, g.max_blocks), NO_PAGE, dtype=torch.int32).pin_memory()
                 g.table = g.table_pinned.numpy()
             for j, ei in enumerate(g.entries):
-                self.views[ei] = KVLayerView(g.storage[j, 0], g.storage[j, 1] if s.values else None, g.table_dev,
-                                             self.block_size, g.window, g.index)
+                values = None if not s.values else (g.value_storage[j] if own_values else g.storage[j, 1])
+                self.views[ei] = KVLayerView(g.storage[j, 0], values, g.table_dev, self.block_size, g.window, g.index)
         for ei, spec in self._state_entries.items():
             t = torch.zeros((self.max_slots, *spec.shape), dtype=getattr(torch, spec.dtype), device=dev)
             self.state[ei] = t
@@ -258,7 +268,7 @@ class CacheManager:
         if not self.live[slot]:
             raise MemoryError_(f"slot {slot} freed twice or never admitted")
         for g in self.groups:
-            for b in range(g.first_live[slot], g.n_blocks[slot]):
+            for b in range(0 if g.keep_blocks else g.first_live[slot], g.n_blocks[slot]):    # kept first blocks too
                 p = int(g.table[slot, b])
                 if p != NO_PAGE:
                     g.pool.release(p, slot)
@@ -328,7 +338,7 @@ class CacheManager:
             if g.window is None:
                 continue
             keep_from = min(g._first_needed_block(new_len), g.n_blocks[slot])
-            for b in range(g.first_live[slot], keep_from):
+            for b in range(max(g.first_live[slot], g.keep_blocks), keep_from):
                 p = int(g.table[slot, b])
                 if p != NO_PAGE:
                     g.pool.release(p, slot)
@@ -367,7 +377,7 @@ class CacheManager:
         self._hashed.pop(slot, None)
         for g in self.groups:
             keep = -(-new_len // g.block_size)           # >= first_live when new_len > 0 (checked above)
-            for b in range(max(keep, g.first_live[slot]), g.n_blocks[slot]):
+            for b in range(keep, g.n_blocks[slot]):           # (blocks already given back hold no page)
                 p = int(g.table[slot, b])
                 if p != NO_PAGE:
                     g.pool.release(p, slot)
@@ -461,7 +471,8 @@ class CacheManager:
                 for b, p in enumerate(row):
                     if p == NO_PAGE:
                         continue
-                    assert g.first_live[slot] <= b < g.n_blocks[slot], f"page outside live range in slot {slot}"
+                    assert (g.first_live[slot] <= b or b < g.keep_blocks) and b < g.n_blocks[slot], \
+                        f"page outside live range in slot {slot}"
                     held.setdefault(int(p), set()).add(slot)
             pool = g.pool
             for p in range(pool.num_pages):

@@ -1,8 +1,9 @@
 from .model_config import LlamaConfig, RopeScaling, read_config_json
 from .sepirax_config import SepiraxConfig
+from .vasonex_config import VasonexConfig
 from .engine_config import EngineConfig
 from .registry import (architecture, architecture_of, known_architectures,
                        register_architecture, ArchEntry)
 
-__all__ = ["LlamaConfig", "SepiraxConfig", "RopeScaling", "read_config_json", "EngineConfig", "architecture",
+__all__ = ["LlamaConfig", "SepiraxConfig", "VasonexConfig", "RopeScaling", "read_config_json", "EngineConfig", "architecture",
            "architecture_of", "known_architectures", "register_architecture", "ArchEntry"]

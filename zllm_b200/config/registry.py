@@ -69,7 +69,7 @@ def _ensure_builtin():
     functions, and the command line, ``bin/trace_run`` and the Python entry points then take its
     model folders like any other."""
     global _plugins_loaded
-    from ..models import llama, sepirax  # noqa: F401
+    from ..models import llama, sepirax, vasonex  # noqa: F401
     if not _plugins_loaded:
         _plugins_loaded = True
         import importlib

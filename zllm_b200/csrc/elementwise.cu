@@ -1,4 +1,5 @@
-// Row-wise kernels: embedding gather (with a scale), RMSNorm, Dynamic Tanh, SiLU-mul, row
+// Row-wise kernels: embedding gather (with a scale), RMSNorm (also of a branch's output, added to the
+// residual), Dynamic Tanh, SiLU-mul (also with biases), row
 // gather, the soft cap of logits, rotary encoding fused with the write of keys and values
 // into cache pages.
 //
@@ -122,6 +123,81 @@ ZLLM_API int zllm_rmsnorm(const float* x, const int* rows, const void* w, void* 
     if (w_bf16) return launch_rmsnorm<bf16, float>(x, rows, w, y, T, H, eps, s);
     if (out_bf16) return launch_rmsnorm<float, bf16>(x, rows, w, y, T, H, eps, s);
     return launch_rmsnorm<float, float>(x, rows, w, y, T, H, eps, s);
+}
+
+// ---------------------------------------------------------------- rmsnorm of a branch, added to the residual
+// residual[t] += (y[t] + b) * rsqrt(mean((y[t] + b)^2) + eps) * w : the norm of a branch's OUTPUT on its way into
+// the residual sum, in one pass.  y and residual float32 [T,H]; b (may be null) float32 [H], a bias the branch
+// left for this pass; w float32 or bf16.  The order of the row's sum is fixed by the block's layout alone.
+template <typename WT>
+__global__ void __launch_bounds__(256) rmsnorm_add_kernel(const float* y, const float* __restrict__ b, const WT* __restrict__ w,
+                                                          float* residual, int H, float eps) {
+    __shared__ float red[33];
+    pdl_trigger();
+    pdl_wait();
+    const float* yr = y + (size_t)blockIdx.x * H;
+    float* xr = residual + (size_t)blockIdx.x * H;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        const float v = yr[i] + (b != nullptr ? b[i] : 0.f);
+        ss += v * v;
+    }
+    ss = block_sum(ss, red);
+    const float inv = rsqrtf(ss / (float)H + eps);
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        const float v = yr[i] + (b != nullptr ? b[i] : 0.f);
+        xr[i] += v * inv * to_f32(w[i]);
+    }
+}
+
+ZLLM_API int zllm_rmsnorm_add(const float* y, const float* bias, const void* w, float* residual, int T, int H, float eps,
+                              int w_bf16, void* stream) {
+    if (T <= 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int th = H >= 1024 ? 256 : 128;
+    if (w_bf16) return launch_pdl(rmsnorm_add_kernel<bf16>, dim3(T), dim3(th), 0, s, y, bias, (const bf16*)w, residual, H, eps);
+    return launch_pdl(rmsnorm_add_kernel<float>, dim3(T), dim3(th), 0, s, y, bias, (const float*)w, residual, H, eps);
+}
+
+// ---------------------------------------------------------------- biases
+// x[t][c] += b[c], float32: a bias on a branch's result that nothing else adds.
+__global__ void add_bias_kernel(float* x, const float* __restrict__ b, int H, size_t n) {
+    pdl_trigger();
+    pdl_wait();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) x[i] += b[i % (size_t)H];
+}
+
+ZLLM_API int zllm_add_bias(float* x, const float* b, int T, int H, void* stream) {
+    if (T <= 0) return 0;
+    const size_t n = (size_t)T * H;
+    return launch_pdl(add_bias_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, (cudaStream_t)stream, x, b, H, n);
+}
+
+// out[t][j] = silu(gu[t][j] + b[j]) * (gu[t][I + j] + b[I + j]) : gu [T, ld] holds the gate columns, then the up
+// columns (ld >= 2I); b float32 [2I].
+template <typename AT>
+__global__ void bias_silu_mul_kernel(const AT* gu, int ld, const float* __restrict__ b, AT* out, int I, size_t n) {
+    pdl_trigger();
+    pdl_wait();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) {
+        const size_t t = i / (size_t)I;
+        const int j = (int)(i - t * (size_t)I);
+        const float g = to_f32(gu[t * ld + j]) + b[j];
+        const float u = to_f32(gu[t * ld + I + j]) + b[I + j];
+        out[i] = from_f32<AT>(g / (1.f + expf(-g)) * u);
+    }
+}
+
+ZLLM_API int zllm_bias_silu_mul(const void* gu, int ld, const float* b, void* out, int T, int I, int is_bf16, void* stream) {
+    if (T <= 0 || I <= 0) return 0;
+    if (ld < 2 * I) return ZLLM_ERR_UNSUPPORTED;
+    const size_t n = (size_t)T * I;
+    const unsigned blocks = (unsigned)((n + 255) / 256);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (is_bf16) return launch_pdl(bias_silu_mul_kernel<bf16>, dim3(blocks), dim3(256), 0, s, (const bf16*)gu, ld, b, (bf16*)out, I, n);
+    return launch_pdl(bias_silu_mul_kernel<float>, dim3(blocks), dim3(256), 0, s, (const float*)gu, ld, b, (float*)out, I, n);
 }
 
 // ---------------------------------------------------------------- dynamic tanh

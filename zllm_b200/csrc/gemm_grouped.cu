@@ -4,7 +4,10 @@
 //               optionally times sigmoid(gate[t][g*N + n]) * out_scale: an output gate.
 //   per expert: rows are (token, choice) pairs sorted by their expert; expert e owns the sorted
 //               range off[e]..off[e+1]-1; sorted entry i stands for pair perm[i].
-//               first product:   act[i][n]      = silu(x[perm[i]/top] . Wg[e][n]) * (x[perm[i]/top] . Wu[e][n])
+//               first product:   act[i][n]      = silu(c x[perm[i]/top] . Wg[e][n]) * (c x[perm[i]/top] . Wu[e][n])   (gated)
+//                           or   act[i][n]      = f(c x[perm[i]/top] . Wu[e][n]),  f = silu, gelu (erf) or gelu (tanh)
+//                                c = row_scale[perm[i]] for the first n_scaled choices of a token, else 1: a router
+//                                weight that multiplies what the expert READS (applied to the float32 sums)
 //               second product:  y[perm[i]][n]  = act[i] . Wd[e][n]
 //
 // Every output element is accumulated by one thread over k = 0..K-1 in that order, so its
@@ -13,6 +16,16 @@
 
 #define GB 64        // tile rows and columns
 #define GK 16
+
+// activations of an expert without a gate matrix
+#define ACT_SILU 0
+#define ACT_GELU 1
+#define ACT_GELU_TANH 2
+__device__ __forceinline__ float expert_act(float z, int act) {
+    if (act == ACT_GELU) return 0.5f * z * (1.f + erff(z * 0.70710678118654752440f));
+    if (act == ACT_GELU_TANH) return 0.5f * z * (1.f + tanhf(0.79788456080286535588f * (z + 0.044715f * z * z * z)));
+    return z / (1.f + expf(-z));
+}
 
 // The inner tile: 256 threads, 4x4 outputs each; a(r, k) and b(c, k) fetch operand elements.
 template <bool DUAL, typename FA, typename FB, typename FU>
@@ -108,7 +121,8 @@ ZLLM_API int zllm_gemm_heads(const void* x, int ldx, int xg, const void* w, void
 template <typename AT, typename OT, bool SWIGLU>
 __global__ void __launch_bounds__(256) gemm_experts_kernel(const AT* x, const AT* __restrict__ w, const AT* __restrict__ wu, OT* out,
                                                            const int* off, const int* perm, int top, int gather,
-                                                           int scatter, int E, int N, int K) {
+                                                           int scatter, int E, int N, int K, const float* row_scale,
+                                                           int n_scaled, int act) {
     __shared__ int s_e, s_row0;
     pdl_trigger();
     pdl_wait();
@@ -145,37 +159,50 @@ __global__ void __launch_bounds__(256) gemm_experts_kernel(const AT* x, const AT
         const int r = row0 + ty * 4 + i;
         if (r >= row_end) continue;
         const size_t orow = scatter ? (size_t)perm[r] : (size_t)r;
+        float c = 1.f;
+        if (gather && row_scale != nullptr && perm[r] % top < n_scaled) c = row_scale[perm[r]];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const int n = n0 + tx * 4 + j;
             if (n >= N) continue;
-            float v = acc[i][j];
-            if (SWIGLU) v = v / (1.f + expf(-v)) * accu[i][j];
+            float v = acc[i][j] * c;
+            if (SWIGLU) v = v / (1.f + expf(-v)) * (accu[i][j] * c);
+            else if (gather) v = expert_act(v, act);
             out[orow * N + n] = from_f32<OT>(v);
         }
     }
 }
 
-// n_pairs = tokens * top sorted entries.  swiglu != 0: w and wu are the experts' gate and up
-// matrices [E, N, K], rows of x are gathered (x[perm[i] / top]), out [n_pairs, N] in sorted
-// order, of x's dtype.  swiglu == 0: x [n_pairs, K] in sorted order, out [n_pairs, N] float32
-// scattered to perm[i].
+// n_pairs = tokens * top sorted entries.
+// mode 1 (gated first product): w and wu are the experts' gate and up matrices [E, N, K], rows of x are
+//   gathered (x[perm[i] / top]), out [n_pairs, N] in sorted order, of x's dtype.
+// mode 2 (first product without a gate): the same with w alone and the activation ``act``.
+// mode 0 (second product): x [n_pairs, K] in sorted order, out [n_pairs, N] float32 scattered to perm[i].
+// row_scale (may be null) [n_pairs] by pair: multiplies the input of the first n_scaled choices of every token.
 ZLLM_API int zllm_gemm_experts(const void* x, const void* w, const void* wu, void* out, const int* off, const int* perm,
-                               int top, int n_pairs, int E, int N, int K, int swiglu, int is_bf16, void* stream) {
+                               int top, int n_pairs, int E, int N, int K, int mode, const float* row_scale, int n_scaled,
+                               int act, int is_bf16, void* stream) {
     if (n_pairs <= 0 || N <= 0) return 0;
-    if (K <= 0 || E <= 0 || top <= 0) return ZLLM_ERR_UNSUPPORTED;
+    if (K <= 0 || E <= 0 || top <= 0 || mode < 0 || mode > 2 || act < 0 || act > 2) return ZLLM_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
     dim3 grid((N + GB - 1) / GB, (n_pairs + GB - 1) / GB + E);
-    if (swiglu) {
+    if (mode == 1) {
         if (is_bf16)
             return launch_pdl(gemm_experts_kernel<bf16, bf16, true>, grid, dim3(256), 0, s, (const bf16*)x, (const bf16*)w,
-                              (const bf16*)wu, (bf16*)out, off, perm, top, 1, 0, E, N, K);
+                              (const bf16*)wu, (bf16*)out, off, perm, top, 1, 0, E, N, K, row_scale, n_scaled, act);
         return launch_pdl(gemm_experts_kernel<float, float, true>, grid, dim3(256), 0, s, (const float*)x, (const float*)w,
-                          (const float*)wu, (float*)out, off, perm, top, 1, 0, E, N, K);
+                          (const float*)wu, (float*)out, off, perm, top, 1, 0, E, N, K, row_scale, n_scaled, act);
+    }
+    if (mode == 2) {
+        if (is_bf16)
+            return launch_pdl(gemm_experts_kernel<bf16, bf16, false>, grid, dim3(256), 0, s, (const bf16*)x, (const bf16*)w,
+                              (const bf16*)nullptr, (bf16*)out, off, perm, top, 1, 0, E, N, K, row_scale, n_scaled, act);
+        return launch_pdl(gemm_experts_kernel<float, float, false>, grid, dim3(256), 0, s, (const float*)x, (const float*)w,
+                          (const float*)nullptr, (float*)out, off, perm, top, 1, 0, E, N, K, row_scale, n_scaled, act);
     }
     if (is_bf16)
         return launch_pdl(gemm_experts_kernel<bf16, float, false>, grid, dim3(256), 0, s, (const bf16*)x, (const bf16*)w,
-                          (const bf16*)nullptr, (float*)out, off, perm, top, 0, 1, E, N, K);
+                          (const bf16*)nullptr, (float*)out, off, perm, top, 0, 1, E, N, K, (const float*)nullptr, 0, 0);
     return launch_pdl(gemm_experts_kernel<float, float, false>, grid, dim3(256), 0, s, (const float*)x, (const float*)w,
-                      (const float*)nullptr, (float*)out, off, perm, top, 0, 1, E, N, K);
+                      (const float*)nullptr, (float*)out, off, perm, top, 0, 1, E, N, K, (const float*)nullptr, 0, 0);
 }

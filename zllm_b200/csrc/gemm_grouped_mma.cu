@@ -3,8 +3,11 @@
 // Same interface as the per-expert kernel of gemm_grouped.cu: rows are (token, choice) pairs sorted
 // by expert, expert e owns the sorted range off[e]..off[e+1]-1, sorted entry i stands for pair
 // perm[i].  A CTA takes a tile of 128 sorted rows of ONE expert and 128 weight rows:
-//   first product  (swiglu): 64 gate rows and the 64 up rows of the same outputs; the rows of x are
+//   first product  (gated):  64 gate rows and the 64 up rows of the same outputs; the rows of x are
 //                  gathered (x[perm[i] / top]); act[i][n] = silu(gate) * up in bfloat16;
+//   first product  (no gate): 128 rows of the one matrix, rows of x gathered; act[i][n] = f(sum), f one of silu,
+//                  gelu (erf), gelu (tanh); in both forms the float32 sums of the first n_scaled choices of a
+//                  token are multiplied by the pair's router weight first (a weight on the expert's input);
 //   second product:          128 rows of the down matrix; y[perm[i]][n] in float32 (scattered).
 // K runs in pieces of 64 or 32 through a three-stage cp.async ring; fragments come from shared memory with
 // ldmatrix and go to mma.sync m16n8k16; eight warps as 4 x 2, each 32 rows x 64 columns.  Every
@@ -85,10 +88,24 @@ __device__ __forceinline__ void tile_mainloop(bf16* As, bf16* Bs, const bf16* (&
     cp_async_wait<0>();
 }
 
-template <bool SWIGLU, int TK, int STAGES>
+#define ACT_SILU 0
+#define ACT_GELU 1
+#define ACT_GELU_TANH 2
+__device__ __forceinline__ float expert_act(float z, int act) {
+    if (act == ACT_GELU) return 0.5f * z * (1.f + erff(z * 0.70710678118654752440f));
+    if (act == ACT_GELU_TANH) return 0.5f * z * (1.f + tanhf(0.79788456080286535588f * (z + 0.044715f * z * z * z)));
+    return z / (1.f + expf(-z));
+}
+
+// MODE 0: second product (rows in sorted order, float32 rows scattered); 1: gated first product; 2: first product
+// with one matrix and an activation (both gather their rows)
+template <int MODE, int TK, int STAGES>
 __global__ void __launch_bounds__(256) gemm_experts_mma_kernel(const bf16* x, const bf16* __restrict__ w,
                                                                const bf16* __restrict__ wu, void* out, const int* off,
-                                                               const int* perm, int top, int E, int N, int K) {
+                                                               const int* perm, int top, int E, int N, int K,
+                                                               const float* row_scale, int n_scaled, int act) {
+    constexpr bool SWIGLU = MODE == 1;
+    constexpr bool GATHER = MODE != 0;
     constexpr int LDS = TK + 8, PIECES = TK / 8, PER_THREAD = TM * PIECES / 256;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* As = reinterpret_cast<bf16*>(smem_raw);            // [STAGES][TM][LDS]
@@ -142,7 +159,7 @@ __global__ void __launch_bounds__(256) gemm_experts_mma_kernel(const bf16* x, co
         int ri = row0 + r;
         a_live[i] = ri < row_end;                            // rows beyond the expert's range are neither loaded nor stored:
         if (ri >= row_end) ri = row0;                        // what a product makes of them stays in rows nobody reads
-        const size_t src = SWIGLU ? (size_t)(perm[ri] / top) : (size_t)ri;
+        const size_t src = GATHER ? (size_t)(perm[ri] / top) : (size_t)ri;
         a_src[i] = x + src * K + kc * 8;
         int n;
         const bf16* base;
@@ -162,6 +179,11 @@ __global__ void __launch_bounds__(256) gemm_experts_mma_kernel(const bf16* x, co
         for (int half = 0; half < 2; ++half) {
             const int r = row0 + wm * 32 + mt * 16 + (lane >> 2) + half * 8;
             if (r >= row_end) continue;
+            float cs = 1.f;
+            if (GATHER && row_scale != nullptr) {
+                const int pr = perm[r];
+                if (pr % top < n_scaled) cs = row_scale[pr];
+            }
             if (SWIGLU) {
                 bf16* orow = reinterpret_cast<bf16*>(out) + (size_t)r * N;
 #pragma unroll
@@ -170,8 +192,17 @@ __global__ void __launch_bounds__(256) gemm_experts_mma_kernel(const bf16* x, co
                     for (int c = 0; c < 2; ++c) {
                         const int n = n0 + wn * 32 + nt * 8 + 2 * (lane & 3) + c;
                         if (n >= N) continue;
-                        const float g = acc[mt][nt][half * 2 + c], u = acc[mt][nt + 4][half * 2 + c];
+                        const float g = acc[mt][nt][half * 2 + c] * cs, u = acc[mt][nt + 4][half * 2 + c] * cs;
                         orow[n] = __float2bfloat16_rn(g / (1.f + expf(-g)) * u);
+                    }
+            } else if (GATHER) {
+                bf16* orow = reinterpret_cast<bf16*>(out) + (size_t)r * N;
+#pragma unroll
+                for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+                    for (int c = 0; c < 2; ++c) {
+                        const int n = n0 + wn * 64 + nt * 8 + 2 * (lane & 3) + c;
+                        if (n < N) orow[n] = __float2bfloat16_rn(expert_act(acc[mt][nt][half * 2 + c] * cs, act));
                     }
             } else {
                 float* orow = reinterpret_cast<float*>(out) + (size_t)perm[r] * N;
@@ -186,12 +217,16 @@ __global__ void __launch_bounds__(256) gemm_experts_mma_kernel(const bf16* x, co
         }
 }
 
-// As zllm_gemm_experts (gemm_grouped.cu) for bfloat16: swiglu != 0: out = act [n_pairs, N] bfloat16
-// in sorted order from gathered rows of x; swiglu == 0: out = y [n_pairs, N] float32 scattered.
+// As zllm_gemm_experts (gemm_grouped.cu) for bfloat16: modes 1 and 2: out = act [n_pairs, N] bfloat16
+// in sorted order from gathered rows of x; mode 0: out = y [n_pairs, N] float32 scattered.
 ZLLM_API int zllm_gemm_experts_mma(const void* x, const void* w, const void* wu, void* out, const int* off, const int* perm,
-                                   int top, int n_pairs, int E, int N, int K, int swiglu, void* stream) {
+                                   int top, int n_pairs, int E, int N, int K, int mode, const float* row_scale, int n_scaled,
+                                   int act, void* stream) {
     if (n_pairs <= 0 || N <= 0) return 0;
-    if (K <= 0 || (K % 32) || E <= 0 || top <= 0 || (((uintptr_t)x | (uintptr_t)w | (uintptr_t)wu) & 15)) return ZLLM_ERR_UNSUPPORTED;
+    if (K <= 0 || (K % 32) || E <= 0 || top <= 0 || mode < 0 || mode > 2 || act < 0 || act > 2 ||
+        (((uintptr_t)x | (uintptr_t)w | (uintptr_t)wu) & 15))
+        return ZLLM_ERR_UNSUPPORTED;
+    const int swiglu = mode == 1;
     cudaStream_t s = (cudaStream_t)stream;
     // pieces of 64 wherever K allows: measured at 2,048 rows of 32 experts 0.44 against 0.50 ms per layer, and at few
     // rows the wider pieces keep more weights in flight
@@ -200,21 +235,25 @@ ZLLM_API int zllm_gemm_experts_mma(const void* x, const void* w, const void* wu,
     static bool raised = false;
     if (!raised) {
         const int big = 3 * (TM + TN) * 72 * (int)sizeof(bf16), small = 3 * (TM + TN) * 40 * (int)sizeof(bf16);
-        cudaError_t e = cudaFuncSetAttribute(gemm_experts_mma_kernel<true, 32, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, small);
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_experts_mma_kernel<false, 32, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, small);
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_experts_mma_kernel<true, 64, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_experts_mma_kernel<false, 64, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
+        cudaError_t e = cudaSuccess;
+#define GE_ATTR(MD) \
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_experts_mma_kernel<MD, 32, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, small); \
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_experts_mma_kernel<MD, 64, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
+        GE_ATTR(0) GE_ATTR(1) GE_ATTR(2)
+#undef GE_ATTR
         if (e != cudaSuccess) return (int)e;
         raised = true;
     }
     const int n_cols = swiglu ? TN / 2 : TN;
     dim3 grid((N + n_cols - 1) / n_cols, (n_pairs + TM - 1) / TM + E);
-#define GE_GO(SW, TKV, STV) return launch_pdl(gemm_experts_mma_kernel<SW, TKV, STV>, grid, dim3(256), smem, s, (const bf16*)x, \
-                                              (const bf16*)w, (const bf16*)wu, out, off, perm, top, E, N, K)
-    if (swiglu && few) GE_GO(true, 64, 3);
-    if (swiglu) GE_GO(true, 32, 3);
-    if (few) GE_GO(false, 64, 3);
-    GE_GO(false, 32, 3);
+#define GE_GO(MD, TKV, STV) return launch_pdl(gemm_experts_mma_kernel<MD, TKV, STV>, grid, dim3(256), smem, s, (const bf16*)x, \
+                                              (const bf16*)w, (const bf16*)wu, out, off, perm, top, E, N, K, row_scale, n_scaled, act)
+    if (mode == 1 && few) GE_GO(1, 64, 3);
+    if (mode == 1) GE_GO(1, 32, 3);
+    if (mode == 2 && few) GE_GO(2, 64, 3);
+    if (mode == 2) GE_GO(2, 32, 3);
+    if (few) GE_GO(0, 64, 3);
+    GE_GO(0, 32, 3);
 #undef GE_GO
 }
 

@@ -67,7 +67,8 @@ class CudaOps:
     # capture), so the shares are those of serialised launches, as a profiler would show them.
     PROFILED = ("embedding", "rmsnorm", "linear", "linear_normed", "qkv_rope_store", "rope_kv_store", "paged_attention",
                 "silu_mul", "gather_rows", "sample", "topk", "pool_draw", "advance_decode", "dynamic_tanh", "softcap",
-                "latent_prepare", "latent_attention", "linear_heads", "matrix_memory", "moe_route", "moe_experts")
+                "latent_prepare", "latent_attention", "linear_heads", "matrix_memory", "moe_route", "moe_experts",
+                "rmsnorm_add", "add_bias", "bias_silu_mul", "rotate_store_kv", "window_attention")
 
     def _profile_setup(self):
         self._prof_depth = 0
@@ -610,30 +611,43 @@ class CudaOps:
         self.launches += 2
 
     # ---- mixture of experts ------------------------------------------------------
-    def moe_route(self, h, w_router, top, groups, keep, idx, weights):
-        """Per row: softmax router scores, the ``top`` experts among the ``keep`` best of ``groups``
-        groups, their normalised weights."""
+    EXPERT_ACTIVATIONS = {"silu": 0, "gelu": 1, "gelu_tanh": 2}
+
+    def moe_route(self, h, w_router, top, groups, keep, idx, weights, score: str = "softmax", normalise: bool = True,
+                  n_shared: int = 0, shared_gate: bool = False):
+        """Per row: router scores (softmax over the experts, or a sigmoid each), the ``top`` experts among
+        the ``keep`` best of ``groups`` groups, their weights (divided by their sum if ``normalise``).
+        Behind them ``n_shared`` choices that every row has, the experts E, E+1, ..., with the weight 1 or,
+        with ``shared_gate`` (the router matrix then has a row E for it), sigmoid of that row's logit."""
         self._dev(h, w_router, idx, weights)
         T, H = h.shape
-        E = w_router.shape[0]
+        E = w_router.shape[0] - (1 if shared_gate else 0)
+        cols = top + n_shared
         if w_router.shape[1] != H or w_router.dtype != h.dtype or idx.dtype != torch.int32 or weights.dtype != torch.float32 \
-                or tuple(idx.shape) != (T, top) or tuple(weights.shape) != (T, top):
+                or tuple(idx.shape) != (T, cols) or tuple(weights.shape) != (T, cols) or score not in ("softmax", "sigmoid"):
             raise BackendError("moe_route: bad operand types or shapes")
         code = self.lib("moe").zllm_moe_route(_ptr(h), _ptr(w_router), _ptr(idx), _ptr(weights), c_int(T), c_int(H), c_int(E),
-                                              c_int(top), c_int(groups), c_int(keep), c_int(h.dtype == torch.bfloat16),
-                                              self._stream())
+                                              c_int(top), c_int(groups), c_int(keep), c_int(score == "sigmoid"),
+                                              c_int(1 if normalise else 0), c_int(n_shared), c_int(1 if shared_gate else 0),
+                                              c_int(h.dtype == torch.bfloat16), self._stream())
         self._check(code, "moe_route")
 
-    def moe_experts(self, h, idx, weights, w_gate, w_up, w_down, residual, scale, ws):
-        """residual[t] += scale * sum_j weights[t, j] * expert_{idx[t, j]}(h[t]); an expert is
-        down(silu(gate x) * (up x)).  w_gate, w_up [E, F, H], w_down [E, H, F]."""
+    def moe_experts(self, h, idx, weights, w_gate, w_up, w_down, residual, scale, ws, n_input_weighted: int = 0,
+                    activation: str = "silu", accumulate: bool = True):
+        """residual[t] (+)= scale * sum_j a_j * expert_{idx[t, j]}(b_j h[t]).  An expert is
+        down(silu(gate x) * (up x)), or down(f(up x)) when ``w_gate`` is None (f = ``activation``).
+        The first ``n_input_weighted`` choices of a row carry their weight on the expert's input
+        (b_j = weights[t, j], a_j = 1), the others on its output (a_j = weights[t, j], b_j = 1).
+        w_gate, w_up [E, F, H], w_down [E, H, F]."""
         self._dev(h, idx, weights, w_gate, w_up, w_down, residual)
         T, H = h.shape
         top = idx.shape[1]
-        E, F, _ = w_gate.shape
-        if tuple(w_gate.shape) != (E, F, H) or tuple(w_up.shape) != (E, F, H) or tuple(w_down.shape) != (E, H, F) \
-                or residual.dtype != torch.float32 or tuple(residual.shape) != (T, H) \
-                or any(t.dtype != h.dtype for t in (w_gate, w_up, w_down)):
+        E, F, _ = w_up.shape
+        if (w_gate is not None and tuple(w_gate.shape) != (E, F, H)) or tuple(w_up.shape) != (E, F, H) \
+                or tuple(w_down.shape) != (E, H, F) or residual.dtype != torch.float32 or tuple(residual.shape) != (T, H) \
+                or any(t is not None and t.dtype != h.dtype for t in (w_gate, w_up, w_down)) \
+                or activation not in self.EXPERT_ACTIVATIONS or not 0 <= n_input_weighted <= top \
+                or tuple(weights.shape) != (T, top) or weights.dtype != torch.float32:
             raise BackendError("moe_experts: bad operand types or shapes")
         n = T * top
         off = ws.get("moe_offsets", (1, E + 1), torch.int32, cap=1)
@@ -643,21 +657,28 @@ class CudaOps:
         moe = self.lib("moe")
         is_bf16 = h.dtype == torch.bfloat16
         self._check(moe.zllm_moe_sort(_ptr(idx), _ptr(off), _ptr(perm), c_int(n), c_int(E), self._stream()), "moe_sort")
+        first_mode = 1 if w_gate is not None else 2
+        first = (w_gate, w_up) if w_gate is not None else (w_up, None)
+        rs = weights if n_input_weighted > 0 else None
+        act_code = self.EXPERT_ACTIVATIONS[activation]
         # each product goes to the tensor-core kernel when its K allows (bfloat16, K a multiple of 32),
         # else to the CUDA-core kernel: decided by the sizes alone
-        for x_in, w_a, w_b, dst, N, K, swiglu in ((h, w_gate, w_up, act, F, H, 1), (act, w_down, None, y, H, F, 0)):
+        for x_in, w_a, w_b, dst, N, K, mode, scale_rows in ((h, first[0], first[1], act, F, H, first_mode, rs),
+                                                            (act, w_down, None, y, H, F, 0, None)):
             if is_bf16 and K % self.EXPERT_MMA_K == 0 and (x_in.data_ptr() | w_a.data_ptr() | (w_b.data_ptr() if w_b is not None else 0)) & 15 == 0:
                 code = self.lib("gemm_grouped_mma").zllm_gemm_experts_mma(
                     _ptr(x_in), _ptr(w_a), _ptr(w_b), _ptr(dst), _ptr(off), _ptr(perm), c_int(top), c_int(n), c_int(E), c_int(N),
-                    c_int(K), c_int(swiglu), self._stream())
+                    c_int(K), c_int(mode), _ptr(scale_rows), c_int(n_input_weighted), c_int(act_code), self._stream())
                 self._check(code, "gemm_experts_mma")
             else:
                 code = self.lib("gemm_grouped").zllm_gemm_experts(
                     _ptr(x_in), _ptr(w_a), _ptr(w_b), _ptr(dst), _ptr(off), _ptr(perm), c_int(top), c_int(n), c_int(E), c_int(N),
-                    c_int(K), c_int(swiglu), c_int(is_bf16), self._stream())
+                    c_int(K), c_int(mode), _ptr(scale_rows), c_int(n_input_weighted), c_int(act_code), c_int(is_bf16),
+                    self._stream())
                 self._check(code, "gemm_experts")
         self._check(moe.zllm_moe_combine(_ptr(y), _ptr(weights), _ptr(residual), c_int(T), c_int(H), c_int(top),
-                                         c_float(scale), self._stream()), "moe_combine")
+                                         c_float(scale), c_int(n_input_weighted), c_int(0 if accumulate else 1), self._stream()),
+                    "moe_combine")
 
     # ---- silu * up -----------------------------------------------------
     def silu_mul(self, a, b, out):
@@ -678,6 +699,89 @@ class CudaOps:
         code = self.lib("elementwise").zllm_gather_rows(_ptr(x), _ptr(rows), _ptr(out), c_int(R), c_int(H),
                                                         self._stream())
         self._check(code, "gather_rows")
+
+    # ---- a branch's output norm, biases ------------------------------------------------
+    def rmsnorm_add(self, y, bias, weight, eps, residual):
+        """residual += rmsnorm(y + bias) * weight, float32; ``bias`` may be None."""
+        self._dev(y, bias, weight, residual)
+        T, H = residual.shape
+        if y.dtype != torch.float32 or residual.dtype != torch.float32 or tuple(y.shape) != (T, H) or weight.numel() != H \
+                or weight.dtype not in (torch.float32, torch.bfloat16) \
+                or (bias is not None and (bias.dtype != torch.float32 or bias.numel() != H)):
+            raise BackendError("rmsnorm_add: bad operand types or shapes")
+        code = self.lib("elementwise").zllm_rmsnorm_add(_ptr(y), _ptr(bias), _ptr(weight), _ptr(residual), c_int(T), c_int(H),
+                                                        c_float(eps), c_int(weight.dtype == torch.bfloat16), self._stream())
+        self._check(code, "rmsnorm_add")
+
+    def add_bias(self, x, bias):
+        """x[t] += bias, float32."""
+        self._dev(x, bias)
+        if x.dtype != torch.float32 or bias.dtype != torch.float32 or bias.numel() != x.shape[1]:
+            raise BackendError("add_bias: bad operand types or shapes")
+        code = self.lib("elementwise").zllm_add_bias(_ptr(x), _ptr(bias), c_int(x.shape[0]), c_int(x.shape[1]), self._stream())
+        self._check(code, "add_bias")
+
+    def bias_silu_mul(self, gu, bias, out):
+        """out = silu(gu[:, :I] + bias[:I]) * (gu[:, I:2I] + bias[I:]); gu [T, >= 2I], bias float32 [2I]."""
+        self._dev(gu, bias, out)
+        T, I = out.shape
+        if gu.dtype != out.dtype or gu.shape[0] != T or gu.shape[1] < 2 * I or bias.dtype != torch.float32 or bias.numel() != 2 * I:
+            raise BackendError("bias_silu_mul: bad operand types or shapes")
+        code = self.lib("elementwise").zllm_bias_silu_mul(_ptr(gu), c_int(gu.shape[1]), _ptr(bias), _ptr(out), c_int(T), c_int(I),
+                                                          c_int(gu.dtype == torch.bfloat16), self._stream())
+        self._check(code, "bias_silu_mul")
+
+    # ---- attention with a window that keeps the first positions ----------------------------
+    def _check_window_cache(self, cache, nkv, dk, dv, dtype, what):
+        kp, vp = cache.k_pages, cache.v_pages
+        self._dev(kp, vp, cache.block_table)
+        if kp.dtype != dtype or vp.dtype != dtype or tuple(kp.shape[1:]) != (nkv, cache.block_size, dk) \
+                or tuple(vp.shape[1:]) != (nkv, cache.block_size, dv) or vp.shape[0] != kp.shape[0] \
+                or cache.block_table.dtype != torch.int32:
+            raise BackendError(f"{what}: cache pages {tuple(kp.shape)} / {tuple(vp.shape)} {kp.dtype} do not match "
+                               f"(kv heads {nkv}, block {cache.block_size}, key size {dk}, value size {dv}, {dtype})")
+
+    def rotate_store_kv(self, proj, off_k, off_v, ctx, freqs, cache, nq, nkv, dk, dv, write_cache=True):
+        """The queries (columns 0..) and keys (from ``off_k``) of ``proj`` rotated in place over their first
+        ``freqs.dims`` entries by position * frequency; keys and values (from ``off_v``) written to their pages.
+        ``freqs``: a ``RotaryFrequencies`` (frequencies on the device, magnitude, dims, pairing) or None."""
+        self._dev(proj, ctx.positions, ctx.row_slot)
+        T, ld = proj.shape
+        if ctx.positions.numel() != T or ctx.row_slot.numel() != T or off_v + nkv * dv > ld:
+            raise BackendError("rotate_store_kv: the projection does not match the head counts or the step's rows")
+        if freqs is not None:
+            self._dev(freqs.freq)
+            if freqs.freq.dtype != torch.float32 or freqs.freq.numel() * 2 != freqs.dims or freqs.dims > dk:
+                raise BackendError("rotate_store_kv: the frequencies do not match the rotated entries")
+        if write_cache:
+            self._check_window_cache(cache, nkv, dk, dv, proj.dtype, "rotate_store_kv")
+            kp, vp, tb, mb, bs = cache.k_pages, cache.v_pages, cache.block_table, cache.block_table.shape[1], cache.block_size
+        else:
+            kp = vp = tb = None
+            mb, bs = 1, 1
+        code = self.lib("attention_window").zllm_rotate_store_kv(
+            _ptr(proj), c_int(ld), c_int(off_k), c_int(off_v), _ptr(ctx.positions), _ptr(ctx.row_slot),
+            _ptr(freqs.freq if freqs is not None else None), c_float(freqs.magnitude if freqs is not None else 1.0),
+            c_int(freqs.dims if freqs is not None else 0), c_int(int(freqs.interleaved) if freqs is not None else 0),
+            _ptr(kp), _ptr(vp), _ptr(tb), c_int(mb), c_int(bs), c_int(T), c_int(nq), c_int(nkv), c_int(dk), c_int(dv),
+            c_int(1 if write_cache else 0), c_int(proj.dtype == torch.bfloat16), self._stream())
+        self._check(code, "rotate_store_kv")
+
+    def window_attention(self, proj, off_g, out, ctx, cache, nq, nkv, dk, dv, scale, window, keep_first):
+        """out[t, a] = sigmoid(gate)(t, a) * sum_j softmax_j(scale q(t, a) . k_j) v_j over the keys j <= the row's
+        position with (position - j < window or j < keep_first); ``window`` None: all of them; ``off_g`` < 0:
+        no gates.  Queries at the front of ``proj``, gate logits at column ``off_g``."""
+        self._dev(proj, out, ctx.positions, ctx.row_slot)
+        T, ld = proj.shape
+        self._check_window_cache(cache, nkv, dk, dv, proj.dtype, "window_attention")
+        if tuple(out.shape) != (T, nq * dv) or out.dtype != proj.dtype or nq * dk > ld:
+            raise BackendError("window_attention: output does not match")
+        code = self.lib("attention_window").zllm_window_attention_plain(
+            _ptr(proj), c_int(ld), c_int(off_g), _ptr(out), _ptr(ctx.positions), _ptr(ctx.row_slot), _ptr(cache.k_pages),
+            _ptr(cache.v_pages), _ptr(cache.block_table), c_int(cache.block_table.shape[1]), c_int(cache.block_size), c_int(T),
+            c_int(nq), c_int(nkv), c_int(dk), c_int(dv), c_float(scale), c_int(window or 0), c_int(keep_first or 0),
+            c_int(proj.dtype == torch.bfloat16), self._stream())
+        self._check(code, "window_attention_plain")
 
     # ---- rotary + cache write ------------------------------------------
     def _check_cache(self, cache, nkv, hd, dtype, what):

@@ -48,7 +48,9 @@ def _build_layers(spec: ModelSpec):
             raise ConfigError(f"unknown arrangement {ls.arrangement!r}")
         has_ffn = ls.ffn is not None
         layers.append(Layer(build("norm", ls.norm1), build("mixer", ls.mixer), build("norm", ls.norm2) if has_ffn else None,
-                            build("feed_forward", ls.ffn) if has_ffn else None, _REGISTRIES["arrangement"][ls.arrangement]))
+                            build("feed_forward", ls.ffn) if has_ffn else None, _REGISTRIES["arrangement"][ls.arrangement],
+                            build("norm", ls.norm1_post) if ls.norm1_post is not None else None,
+                            build("norm", ls.norm2_post) if has_ffn and ls.norm2_post is not None else None))
     final_norm = build("norm", spec.final_norm)
     position = build("position_encoding", spec.embedding_position) if spec.embedding_position is not None else None
     return layers, final_norm, position

@@ -26,6 +26,10 @@ Interfaces (all tensors are torch tensors on the engine's device):
     the cos/sin tables and pairing) and may act on the embedding output.
 ``Block`` arrangement
     given norms, mixer and feed-forward, runs them in its order on the residual.
+
+A mixer or feed-forward whose class sets ``can_overwrite`` also takes ``accumulate=False``: it
+then WRITES its result into the float32 array it is given instead of adding to it (an
+arrangement that norms a branch's output before the residual sum needs the branch alone).
 """
 from __future__ import annotations
 
@@ -77,6 +81,9 @@ class LayerSpec:
     norm2: Optional[PartSpec]
     arrangement: str = "pre_norm"
     tensor_names: Dict[str, str] = field(default_factory=dict)
+    # norms of the branches' OUTPUTS (part names "norm1b", "norm2b"), for arrangements that have them
+    norm1_post: Optional[PartSpec] = None
+    norm2_post: Optional[PartSpec] = None
 
 
 @dataclass
@@ -134,12 +141,17 @@ class ModelSpec:
 class KVCacheSpec:
     """Keys and values of every position (window None) or of the last ``window``.
     ``values`` False: one row per position and head instead of a key row and a value row (a
-    mixer whose values are a part of what it caches as keys, e.g. a shared latent)."""
+    mixer whose values are a part of what it caches as keys, e.g. a shared latent).
+    ``value_dim``: the size of a value row when it differs from a key row's (None: the same).
+    ``keep_first``: with a window, the first positions of a request that stay readable however
+    far the window has moved on; their pages are never given back during the request."""
 
     n_kv_heads: int
     head_dim: int
     window: Optional[int] = None
     values: bool = True
+    value_dim: Optional[int] = None
+    keep_first: int = 0
 
 
 @dataclass(frozen=True)
@@ -191,6 +203,11 @@ class Norm(Part):
     def forward(self, x, out, ctx):
         raise NotImplementedError
 
+    def forward_add(self, y, residual, ctx, bias=None):
+        """residual += norm(y [+ bias]) for a float32 branch output ``y``: the norm of a branch's
+        output on its way into the residual sum.  Norms that can do it in one pass override this."""
+        raise NotImplementedError(f"{type(self).__name__} cannot norm a branch's output")
+
     def as_prologue(self):
         """(weight, eps) if a following product may apply this norm itself (an RMS norm), else None."""
         return None
@@ -210,6 +227,8 @@ class Mixer(Part):
     # True: ``forward`` takes ``input_norm=(weight, eps)`` and then receives the float32 residual
     # itself as ``h`` (it applies the norm inside its first product)
     accepts_input_norm = False
+    # True: ``forward`` takes ``accumulate=False`` and then writes its result instead of adding it
+    can_overwrite = False
 
     def cache_spec(self):
         return None
@@ -220,6 +239,7 @@ class Mixer(Part):
 
 class FeedForward(Part):
     accepts_input_norm = False          # as for Mixer
+    can_overwrite = False               # as for Mixer
 
     def forward(self, h, residual, ctx):
         raise NotImplementedError

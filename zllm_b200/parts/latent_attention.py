@@ -47,6 +47,8 @@ class LatentAttention(Mixer):
             raise ConfigError("latent attention: sizes must be positive")
         if self.dr and position_encoding is None:
             raise ConfigError("latent attention: a rotated part needs a position encoding")
+        if position_encoding is not None and getattr(position_encoding, "interleaved", False):
+            raise ConfigError("latent attention rotates half-split pairs only")
         if position_encoding is not None and position_encoding.dims > self.dr:
             raise ConfigError(f"latent attention: {position_encoding.dims} rotated dimensions exceed rot_dim {self.dr}")
 

@@ -33,6 +33,10 @@ class RMSNorm(Norm):
         """(weight, eps): what a product needs to apply this norm to its own input rows."""
         return (self.weight, self.eps)
 
+    def forward_add(self, y, residual, ctx, bias=None):
+        """residual += rmsnorm(y + bias) * weight in one pass, all float32."""
+        self.rt.ops.rmsnorm_add(y, bias, self.weight, self.eps, residual)
+
 
 @register_norm("dynamic_tanh")
 class DynamicTanh(Norm):

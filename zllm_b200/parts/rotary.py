@@ -128,11 +128,31 @@ def yarn_frequencies(dims: int, base: float, factor: float, original: int, fast:
     return (g / factor * ramp + g * (1.0 - ramp)).to(torch.float32), 0.1 * math.log(factor) + 1.0
 
 
+def stretched_frequencies(dims: int, base: float, factor: float, original: float, low: float, high: float):
+    """The frequencies of the dims/2 pairs with long waves slowed down (the scheme of Llama 3.1).
+
+    g_i = base^(-2i/dims) has the wavelength l_i = 2 pi / g_i.  A wave shorter than original/high keeps
+    its frequency; one longer than original/low gets g_i / factor; in between, with
+    s = (original / l_i - low) / (high - low), the pair gets (1 - s) g_i / factor + s g_i.
+    Computed in double precision and rounded once to float32."""
+    if dims <= 0 or dims % 2:
+        raise ConfigError(f"rotary: dims {dims} must be positive and even")
+    if not high > low:
+        raise ConfigError("rotary scaling: 'high' must exceed 'low'")
+    i = torch.arange(dims // 2, dtype=torch.float64)
+    g = torch.pow(torch.tensor(float(base), dtype=torch.float64), -2.0 * i / dims)
+    wavelength = 2.0 * math.pi / g
+    s = (original / wavelength - low) / (high - low)
+    blend = (1.0 - s) * g / factor + s * g
+    return torch.where(wavelength < original / high, g, torch.where(wavelength > original / low, g / factor, blend)).to(torch.float32)
+
+
 @dataclass
 class RotaryFrequencies:
     freq: torch.Tensor        # [dims/2] float32, on device
     magnitude: float          # multiplies cos and sin
     dims: int
+    interleaved: bool = False  # pairs (2i, 2i+1) instead of (i, i + dims/2)
 
     def as_tuple(self):
         return (self.freq, self.magnitude, self.dims)
@@ -141,17 +161,26 @@ class RotaryFrequencies:
 @register_position_encoding("rotary_on_the_fly")
 class RotaryOnTheFly(PositionEncoding):
     """Rotary encoding without tables: kernels get the pairs' frequencies and compute the angle
-    position * frequency in float32 themselves, so there is no largest position.  Half-split
-    pairing (entry i with entry i + dims/2).  ``scaling`` None, or the YaRN constants
-    {factor, original, fast, slow}."""
+    position * frequency in float32 themselves, so there is no largest position.  Pairing:
+    half-split (entry i with entry i + dims/2) or, with ``interleaved``, neighbours (2i, 2i+1).
+    ``scaling`` None, the YaRN constants {factor, original, fast, slow}, or the constants of the
+    stretching of long waves {factor, original, low, high} (``stretched_frequencies``)."""
 
     capturable = True
 
-    def __init__(self, dims: int, base: float, scaling: Optional[dict] = None):
+    def __init__(self, dims: int, base: float, scaling: Optional[dict] = None, interleaved: bool = False):
         self.dims = int(dims)
         self.base = float(base)
         self.scaling = dict(scaling) if scaling else None
-        if self.scaling:
+        self.interleaved = bool(interleaved)
+        if self.scaling and "low" in self.scaling:
+            for k in ("factor", "original", "low", "high"):
+                if k not in self.scaling:
+                    raise ConfigError(f"rotary scaling is missing key {k!r}")
+            self.freq = stretched_frequencies(self.dims, self.base, float(self.scaling["factor"]), float(self.scaling["original"]),
+                                              float(self.scaling["low"]), float(self.scaling["high"]))
+            self.magnitude = 1.0
+        elif self.scaling:
             for k in ("factor", "original", "fast", "slow"):
                 if k not in self.scaling:
                     raise ConfigError(f"rotary scaling is missing key {k!r}")
@@ -168,7 +197,8 @@ class RotaryOnTheFly(PositionEncoding):
 
     def bind(self, rt):
         super().bind(rt)
-        self._on_device = RotaryFrequencies(self.freq.to(rt.device).contiguous(), float(self.magnitude), self.dims)
+        self._on_device = RotaryFrequencies(self.freq.to(rt.device).contiguous(), float(self.magnitude), self.dims,
+                                            self.interleaved)
 
     def frequencies(self) -> RotaryFrequencies:
         return self._on_device
