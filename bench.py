@@ -7,6 +7,7 @@ bfloat16) on one B200, with prefill throughput, roofline fractions and end-to-en
     python bench.py --config 3b-mixed    # Llama-3.2-3B shape: 32 requests, 512-token portions beside decoding
     python bench.py --config cpu-baseline  # the plain CPU implementation of the test-suite, timed (no GPU)
     python bench.py --config sepirax     # Sepirax at layer sizes of a real model beside Llama layers of equal width
+    python bench.py --config vasonex [--shape vasonex-128]   # Vasonex likewise (heads of 64, or of 128 with values of 96)
 
 One JSON line on stdout.  ``value``: decode tokens/s at batch 8 near context 4096, K decode
 steps timed on the device with CUDA events (the steps replay a captured graph back to back,
@@ -207,24 +208,63 @@ def _sepirax_shape(layers=4, vocab=32000):
             "layers": [{"type": kinds[i % 2][0], "mixer": kinds[i % 2][1], "mlp": moe} for i in range(layers)]}
 
 
-def sepirax_bench(args):
-    """Prefill and decode of Sepirax beside the Llama layers of equal width: milliseconds, tokens/s and the
-    device time per kind of operation (a second pass with per-operation timers, graphs off)."""
-    import torch
-    from zllm_b200 import EngineConfig, LlamaConfig, ModelRunner, StepEntry
-    from zllm_b200.config import SepiraxConfig
-    from zllm_b200.kernels.ops import CudaOps
+# Vasonex at sizes that resemble a real model's layers (random weights): width 2048; attention of 32 heads of 64
+# over 8 key/value heads (the 1B Llama layer's) or of 16 heads of 128 with values of 96 over 4, 32 (64) rotated
+# entries, a window of 1,024 (4,096) that keeps the first 4 positions; layers alternate between a dense
+# feed-forward of 8,192 with biases and 32 experts of 1,024 of which 4 are chosen, plus a shared expert of 2,048.
+def _vasonex_shape(layers=4, vocab=32000, wide=False):
+    sc = {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}
+    if wide:
+        mx = {"heads": 16, "kv_heads": 4, "dim": 128, "vdim": 96, "scale": 128 ** -0.5,
+              "rot": {"dims": 64, "base": 500000.0, "scaling": sc}, "mask": {"size": 4096, "keep_first": 4}}
+    else:
+        mx = {"heads": 32, "kv_heads": 8, "dim": 64, "vdim": 64, "scale": 0.125,
+              "rot": {"dims": 32, "base": 500000.0, "scaling": sc}, "mask": {"size": 1024, "keep_first": 4}}
+    ffs = [{"kind": "dense", "ff": 8192},
+           {"kind": "moe", "expert": {"ff": 1024}, "router": {"experts": 32, "top": 4}, "shared": {"ff": 2048}}]
+    return {"architecture": "Vasonex", "vocab": vocab, "width": 2048, "norm": {"eps": 1e-6},
+            "layers": [{"type": "attention", "mixer": mx, "mlp": ffs[i % 2]} for i in range(layers)]}
 
-    L, V, B, ctx_len = args.layers or 4, 32000, args.batch, args.context
+
+def vasonex_bench(args):
+    """Prefill and decode of Vasonex beside Llama layers of equal width and head sizes."""
+    from zllm_b200 import LlamaConfig
+    from zllm_b200.config import VasonexConfig
+    L, V = args.layers or 4, 32000
+    wide = args.shape == "vasonex-128"
+    heads = dict(num_attention_heads=16, num_key_value_heads=4, head_dim=128) if wide else {}
+    models = {"vasonex": VasonexConfig.from_dict(_vasonex_shape(L, V, wide)),
+              "llama": LlamaConfig.from_dict(dict(MODEL, num_hidden_layers=L, vocab_size=V, tie_word_embeddings=False, **heads))}
+    if args.shape == "vasonex-only":
+        models.pop("llama")
+    return side_by_side_bench(args, "vasonex-128" if wide else "vasonex", models, L, V)
+
+
+def sepirax_bench(args):
+    """Prefill and decode of Sepirax beside the Llama layers of equal width."""
+    from zllm_b200 import LlamaConfig
+    from zllm_b200.config import SepiraxConfig
+    L, V = args.layers or 4, 32000
     models = {"sepirax": SepiraxConfig.from_dict(_sepirax_shape(L, V)),
               "llama": LlamaConfig.from_dict(dict(MODEL, num_hidden_layers=L, vocab_size=V, tie_word_embeddings=False))}
+    if args.shape == "sepirax-only":
+        models.pop("llama")
+    return side_by_side_bench(args, "sepirax", models, L, V)
+
+
+def side_by_side_bench(args, label, models, L, V):
+    """Prefill and decode of every model of ``models`` (name -> typed configuration): milliseconds, tokens/s and the
+    device time per kind of operation (a second pass with per-operation timers, graphs off)."""
+    import torch
+    from zllm_b200 import EngineConfig, ModelRunner, StepEntry
+    from zllm_b200.kernels.ops import CudaOps
+
+    B, ctx_len = args.batch, args.context
     gen = torch.Generator().manual_seed(0)
     rand = lambda n: torch.randint(0, V, (n,), generator=gen).tolist()
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     sizes = (512, 2048) if args.tokens > 0 else ()          # --tokens 0: the decode part only (for a launch list)
-    out = {"config": "sepirax", "layers": L, "batch": B, "context": ctx_len, "dtype": "bf16", "data": "synthetic", "models": {}}
-    if args.shape == "sepirax-only":
-        models.pop("llama")
+    out = {"config": label, "layers": L, "batch": B, "context": ctx_len, "dtype": "bf16", "data": "synthetic", "models": {}}
     for name, cfg in models.items():
         res = {}
         for profiled in ((False,) if args.tokens == 0 else (False, True)):
@@ -410,7 +450,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=32)
     ap.add_argument("--impl", default="ours", choices=("ours", "reference"))
     ap.add_argument("--batch", type=int, default=8)
-    ap.add_argument("--config", default="1b", choices=("1b", "8b", "3b-mixed", "cpu-baseline", "sepirax"),
+    ap.add_argument("--config", default="1b", choices=("1b", "8b", "3b-mixed", "cpu-baseline", "sepirax", "vasonex"),
                     help="which of the configurations the numbers are quoted on (default: the 1B headline)")
     ap.add_argument("--case", default=None, choices=("decode", "prefill"),
                     help="run only a small case for a profiler: a few decode steps without graphs, or one prefill")
@@ -419,8 +459,9 @@ def main():
     ap.add_argument("--layers", type=int, default=None, help="--case: fewer layers (profiling only)")
     ap.add_argument("--graphs", action="store_true", help="--case: with CUDA graphs (default off, so that a profiler sees "
                     "every kernel as its own launch)")
-    ap.add_argument("--shape", default="1b", choices=sorted(SHAPES) + ["sepirax-only"],
-                    help="--case: layer sizes of another Llama shape; --config sepirax: sepirax-only leaves the Llama model out")
+    ap.add_argument("--shape", default="1b", choices=sorted(SHAPES) + ["sepirax-only", "vasonex-128", "vasonex-only"],
+                    help="--case: layer sizes of another Llama shape; --config sepirax: sepirax-only leaves the Llama model out; "
+                         "--config vasonex: vasonex-128 takes heads of 128 with values of 96, vasonex-only leaves the Llama model out")
     args = ap.parse_args()
 
     if args.config == "cpu-baseline":
@@ -445,6 +486,8 @@ def main():
         return mixed_workload(args, K, W)
     if args.config == "sepirax":
         return sepirax_bench(args)
+    if args.config == "vasonex":
+        return vasonex_bench(args)
 
     pk, pk_src = peaks()
     big = args.config == "8b"

@@ -118,14 +118,18 @@ def small_ff(x, w, p):
     return gelu(x @ w[p + "up"].T) @ w[p + "down"].T
 
 
-def mixture(h, w, p, mlp):
+def mixture(h, w, p, mlp, forced=None):
     """Every token goes to its ``top`` best experts by sigmoid score; the score multiplies what the
-    expert reads; a shared expert, if there is one, is added behind a sigmoid gate per token."""
+    expert reads; a shared expert, if there is one, is added behind a sigmoid gate per token.
+    ``forced`` [T, top]: the experts to take instead of the best ones (to follow an implementation
+    through a close call between two scores)."""
     E, top = mlp["router"]["experts"], mlp["router"]["top"]
     score = torch.sigmoid(h @ w[p + "router"].T)                             # [T, E]
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
         order = sorted(range(E), key=lambda e: (-float(score[t, e]), e))[:top]
+        if forced is not None:
+            order = [int(e) for e in forced[t]]
         for e in order:
             out[t] += small_ff(score[t, e] * h[t], w, f"{p}e{e}.")
     if mlp.get("shared"):
@@ -133,13 +137,28 @@ def mixture(h, w, p, mlp):
     return out
 
 
+def router_margin(h, w, p, mlp):
+    """Per token: how far the last chosen expert's router logit lies above the first one not chosen, as a
+    fraction of the token's largest |logit| (infinite when every expert is chosen)."""
+    z = h @ w[p + "router"].T
+    top = mlp["router"]["top"]
+    if top >= z.shape[1]:
+        return torch.full((h.shape[0],), float("inf"), dtype=h.dtype)
+    best = z.sort(-1, descending=True).values
+    return (best[:, top - 1] - best[:, top]) / z.abs().max(-1).values
+
+
 # ---------------------------------------------------------------- the model
-def forward(tokens, cfg, w, want_layers=False, angle_dtype=None):
+def forward(tokens, cfg, w, want_layers=False, angle_dtype=None, want_margins=False, forced=None):
     """logits [T, vocab] of the token list; with ``want_layers`` also the residual stream after
-    every layer run, [runs, T, width]."""
+    every layer run, [runs, T, width]; with ``want_margins`` also, per position, the smallest
+    ``router_margin`` over the layer runs with a mixture (a close call there means that an
+    implementation with other roundings may send the token to another expert).  ``forced``
+    {layer run: [T, top] expert ids}: the choices to take in those runs."""
     eps = cfg["norm"]["eps"]
     x = w["embed"][torch.as_tensor(tokens, dtype=torch.long)]
     streams = []
+    margins = torch.full((len(tokens),), float("inf"), dtype=x.dtype)
     for i, ly in enumerate(cfg["layers"]):
         src = ly.get("weights_of", i)
         src = i if src is None else src
@@ -149,10 +168,13 @@ def forward(tokens, cfg, w, want_layers=False, angle_dtype=None):
         mlp = ly.get("mlp")
         if mlp is not None:
             h = rms_norm(x, w[p + "norm2"], eps)
-            y = gated_ff(h, w, p + "mlp.") if mlp["kind"] == "dense" else mixture(h, w, p + "mlp.", mlp)
+            if mlp["kind"] != "dense" and want_margins:
+                margins = torch.minimum(margins, router_margin(h, w, p + "mlp.", mlp))
+            y = gated_ff(h, w, p + "mlp.") if mlp["kind"] == "dense" else \
+                mixture(h, w, p + "mlp.", mlp, forced[i] if forced is not None else None)
             x = x + rms_norm(y, w[p + "norm2b"], eps)
         streams.append(x)
     logits = rms_norm(x, w["final.norm"], eps) @ w["head"].T
-    if want_layers:
-        return logits, torch.stack(streams)
+    if want_layers or want_margins:
+        return (logits,) + ((torch.stack(streams),) if want_layers else ()) + ((margins,) if want_margins else ())
     return logits

@@ -19,6 +19,68 @@ pytestmark = pytest.mark.gpu
 
 # bounds of the bfloat16 comparisons, as a fraction of the request's largest |logit|, per test model
 BF16_OF_SCALE = {"A": 0.03, "B": 0.03, "C": 0.03, "D": 0.04}
+# A router logit that lies closer to the next one than this fraction of the token's largest is a close call:
+# an implementation with other roundings (bfloat16) may send the token to the other expert, and its logits (and,
+# through attention, those of later positions) are then another function's.  The comparisons therefore follow the
+# engine through its choices: the mixture part records what it chose for every row, the plain implementation is run
+# with those choices, and wherever the plain scores were NOT a close call the engine must have chosen as the plain
+# implementation would.
+CLOSE_CALL = 0.01
+# the bfloat16 engine's router reads a residual stream that has drifted by a percent or so after a few layers:
+# there a margin under 5 % counts as a close call
+CLOSE_CALL_BF16 = 0.05
+
+
+class _Choices:
+    """Collects the experts the engine chose, per (request, layer run), while a trace is replayed."""
+
+    def __init__(self, runner, cfg):
+        self.runs = [i for i, ly in enumerate(cfg["layers"]) if ly.get("mlp") and ly["mlp"]["kind"] == "moe"]
+        self.record = []
+        self.seen = {}                        # (request, run) -> {position: [experts]}
+        for layer in runner.model.layers:
+            if layer.ffn is not None and hasattr(layer.ffn, "record"):
+                layer.ffn.record = self.record
+
+    def after_step(self, step, first):
+        assert len(self.record) == len(self.runs), "one record per layer run with a mixture"
+        for run, (_, _, idx) in zip(self.runs, self.record):
+            idx, r = idx.cpu(), 0
+            for e in step["entries"]:
+                for k in range(len(e["tokens"])):
+                    self.seen.setdefault((e["id"], run), {})[first[e["id"]] + k] = idx[r].tolist()
+                    r += 1
+        self.record.clear()
+
+    def forced(self, rid, n):
+        return {run: torch.tensor([self.seen[(rid, run)][p] for p in range(n)]) for run in self.runs}
+
+
+_FREE = {}                  # (model folder, request) -> (plain logits with the plain choices, router margins)
+
+
+def _compare_following_the_choices(got, choices, cfg, w, reqs, prefix, atol, bound_of_scale, what, key=None, close=CLOSE_CALL):
+    from gpu_util import observe
+    for rid, toks in reqs:
+        forced = choices.forced(prefix + rid, len(toks)) if choices.runs else None
+        ref64 = PV.forward(toks, cfg, w, forced=forced)
+        ref = ref64.float()
+        scale = float(ref.abs().max())
+        for p in range(len(toks)):
+            err = float((got[(prefix + rid, p)] - ref[p]).abs().max())
+            if bound_of_scale > 0:
+                observe(what, err, scale, bound_of_scale)
+            assert err <= atol + bound_of_scale * scale, (f"{what}: request {rid} position {p} (first wrong place): "
+                                                          f"max abs error {err:.3e} > {atol + bound_of_scale * scale:.3e}")
+        if choices.runs:
+            # up to the request's first close call the engine chose what the plain implementation chooses by itself
+            if (key, rid) not in _FREE:
+                _FREE[(key, rid)] = PV.forward(toks, cfg, w, want_margins=True)
+            free, margins = _FREE[(key, rid)]
+            near = (margins < close).nonzero().flatten()
+            first = int(near[0]) if len(near) else len(toks)
+            assert first == 0 or float((ref64[:first] - free[:first]).abs().max()) < 1e-9, \
+                f"{what}: request {rid}: the engine chose other experts than the plain implementation without a close call"
 
 
 @pytest.fixture(scope="module")
@@ -308,20 +370,21 @@ def test_every_way_of_cutting_agrees_with_plain(tmp_path, name, dtype):
     cfg, w = read_dir(d)
     V = cfg["vocab"]
     reqs = [(f"r{i}", random_prompt(V, n, 20 + i)) for i, n in enumerate((5, 41, 33, 270, 1, 17, 64, 65))]
-    ref = {rid: PV.forward(toks, cfg, w).float() for rid, toks in reqs}
     max_tokens = 512
     steps = (TR.family_whole(reqs, "w.") + TR.family_tail(reqs, 40, "t.") + TR.family_portions(reqs, prefix="p.")
              + TR.family_portions(reqs, sizes=(2,), prefix="q.") + TR.family_mixed(reqs, max_tokens, 4, 1, "m.")
              + TR.family_mixed(reqs, max_tokens, 3, 2, "n."))
     bs = VASONEX[name][1]
     runner = _runner(d, name, dtype, max_tokens // bs)
-    got = TR.replay_inprocess(runner, steps)
+    choices = _Choices(runner, cfg)
+    got = TR.replay_inprocess(runner, steps, after_step=choices.after_step)
     runner.ops.check_async_errors()
     for prefix in ("w.", "t.", "p.", "q.", "m.", "n."):
         if dtype == "float32":
-            TR.compare(got, ref, reqs, prefix, 3e-4, 0.0, f"vasonex {name} {prefix} float32")
+            _compare_following_the_choices(got, choices, cfg, w, reqs, prefix, 3e-4, 0.0, f"vasonex {name} {prefix} float32", str(d))
         else:
-            TR.compare(got, ref, reqs, prefix, 0.0, BF16_OF_SCALE[name], f"vasonex {name} {prefix} bfloat16")
+            _compare_following_the_choices(got, choices, cfg, w, reqs, prefix, 0.0, BF16_OF_SCALE[name], f"vasonex {name} {prefix} bfloat16", str(d),
+                                           CLOSE_CALL_BF16)
     if dtype == "float32":
         # the order of every sum is fixed by the position: the ways of cutting agree bit for bit
         for rid, toks in reqs:
@@ -376,9 +439,21 @@ def test_greedy_generation_through_the_engine(tmp_path, name, dtype, graphs):
                  max_num_batched_tokens=48)
     got = eng.generate(prompts, SamplingParams.greedy(max_tokens=24))
     eng.runner.ops.check_async_errors()
+    checked = 0
     for p, o in zip(prompts, got):
-        check_greedy_stream(lambda t: PV.forward(t, cfg, w).float(), p, o, dtype, 24, gap_of_scale=0.04,
-                            what=f"vasonex {name} {dtype} graphs={graphs}")
+        assert len(o) == 24
+        n = 24
+        if dtype == "bfloat16":
+            # behind a close call between two experts the bfloat16 stream may be another function's: it is compared up
+            # to the first one (the float32 streams are compared to their end)
+            _, margins = PV.forward(list(p) + list(o[:-1]), cfg, w, want_margins=True)
+            close = (margins < CLOSE_CALL).nonzero().flatten()
+            n = 24 if not len(close) else max(0, int(close[0]) - len(p) + 1)
+        if n > 0:
+            check_greedy_stream(lambda t: PV.forward(t, cfg, w).float(), p, o[:n], dtype, n, gap_of_scale=0.04,
+                                what=f"vasonex {name} {dtype} graphs={graphs}")
+        checked += n
+    assert checked >= 8                        # (the float32 runs compare all 144)
     # and the same streams again through the same engine: slots, pages and graphs used again
     assert eng.generate(prompts, SamplingParams.greedy(max_tokens=24)) == got
 

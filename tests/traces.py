@@ -112,8 +112,10 @@ def live_tokens_needed(steps):
 
 
 # ---------------------------------------------------------------------------------------
-def replay_inprocess(runner, steps):
-    """Drive a ModelRunner directly; returns {(id, position): logits row (CPU float32)}."""
+def replay_inprocess(runner, steps, after_step=None):
+    """Drive a ModelRunner directly; returns {(id, position): logits row (CPU float32)}.
+    ``after_step(step, first positions)`` is called after every step with the step's description and
+    {id: position of its entry's first token}."""
     from zllm_b200 import StepEntry
     slots, pos, out = {}, {}, {}
     for s in steps:
@@ -132,6 +134,8 @@ def replay_inprocess(runner, steps):
                 for w in e["want"]:
                     out[(e["id"], pos[e["id"]] + w)] = logits[r].clone()
                     r += 1
+        if after_step is not None:
+            after_step(s, {e["id"]: pos[e["id"]] for e in s["entries"]})
         for e in s["entries"]:
             pos[e["id"]] += len(e["tokens"])
         for rid in s["end"]:

@@ -20,8 +20,23 @@
 // fixed by the row's own position: a row's result does not depend on the batch around it, on
 // how its prompt was cut, or on which pages hold its keys.  It serves the 32-bit path and every
 // size; pages that the window has passed (table entry < 0) are never touched.
-#include "common.cuh"
-#include <math.h>
+//
+// bfloat16 with key and value sizes that are multiples of 16 (up to 128) runs on tensor cores
+// (mma.sync m16n8k16, float32 scores, softmax and sums):
+//   prompt portions  one CTA per (tile of 128 query rows of a portion, query head), eight warps of 16
+//                    rows; keys and values come in blocks of 64 through a two-stage cp.async ring,
+//                    gathered through the block table; only the blocks that hold a kept first
+//                    position or a key of the tile's window are visited, and only blocks that touch
+//                    an edge of some row's visibility pay for the masking.
+//   decoded rows     one CTA per (row, kv head); the query heads that share the kv head are the rows of
+//                    the tile, so keys and values are read once for the group; the four warps take the
+//                    visible blocks of 32 keys in turn, each with its own running maximum and sums,
+//                    and merge in warp order at the end.  A window bounds a row's keys, so there are no
+//                    splits over CTAs and no merge kernel.
+// The softmax weights stay 32-bit through the second product: a weight goes to the tensor cores as
+// the sum of two bfloat16 numbers (its rounding and the rounding of what is left), two MMAs per tile.
+#include "attention_common.cuh"
+#include <cuda_pipeline.h>
 
 #define WA_MAX_D 256
 
@@ -188,4 +203,382 @@ ZLLM_API int zllm_window_attention_plain(const void* proj, int ld, int off_g, vo
     return launch_pdl(window_attention_plain_kernel<float>, grid, dim3(128), 0, s, (const float*)proj, ld, off_g, (float*)out,
                       positions, row_slot, (const float*)k_pages, (const float*)v_pages, table, max_blocks, bs, nq, nkv, dk, dv,
                       scale, window, keep_first);
+}
+
+// ---------------------------------------------------------------- tensor cores (bfloat16)
+#define WA_PF_ROWS 128          // query rows of a tile (= the host's QUERY_TILE)
+#define WA_PF_KEYS 64           // keys of a block in prompt portions
+#define WA_DEC_KEYS 32          // keys of a block in decoding
+#define WA_DEC_WARPS 4
+
+template <int VMAX>
+struct WaState {
+    float m[2], l[2];
+    float o[VMAX / 8][4];
+    __device__ __forceinline__ void init() {
+        m[0] = m[1] = -INFINITY;
+        l[0] = l[1] = 0.f;
+#pragma unroll
+        for (int i = 0; i < VMAX / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    }
+};
+
+// NK rows of keys or values (keys key0 .. key0 + NK - 1 of one request and kv head) into a shared tile
+// [NK][str] by 16-byte async copies of NTHR threads; rows beyond ``key_hi`` or without a page become zeros.
+template <int NK, int NTHR>
+__device__ __forceinline__ void wa_gather(bf16* tile, int str, const bf16* pages, const int* __restrict__ trow, int key0,
+                                          int key_hi, int bs, int nkv, int kvh, int d, int tid) {
+    const int chunks = d >> 3;
+    for (int c = tid; c < NK * chunks; c += NTHR) {
+        const int r = c / chunks, ch = c - r * chunks;
+        const int key = key0 + r;
+        bf16* dst = tile + r * str + ch * 8;
+        const bf16* src = nullptr;
+        if (key <= key_hi) {
+            const int blk = key / bs;
+            const int page = trow[blk];
+            if (page >= 0) src = pages + (((size_t)page * nkv + kvh) * bs + (key - blk * bs)) * d + ch * 8;
+        }
+        if (src != nullptr) __pipeline_memcpy_async(dst, src, 16);
+        else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+    }
+}
+
+// Scores of the warp's 16 rows against a block of NB keys.
+template <int KMAX, int NB>
+__device__ __forceinline__ void wa_scores(const unsigned (&qf)[KMAX / 16][4], const bf16* ks, int strk, int nk16, int lane,
+                                          float (&s)[NB / 8][4]) {
+    const int lrow = lane & 7, lmat = lane >> 3;
+#pragma unroll
+    for (int j = 0; j < NB / 8; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+#pragma unroll
+    for (int kk = 0; kk < KMAX / 16; ++kk) {
+        if (kk < nk16) {
+#pragma unroll
+            for (int j = 0; j < NB / 8; j += 2) {
+                // matrices: (keys 8j.., entries 16kk..), (keys 8j.., 16kk+8..), (keys 8j+8.., 16kk..), (.., +8)
+                unsigned b[4];
+                ldmatrix_x4(b, ks + (8 * j + (lmat >> 1) * 8 + lrow) * strk + 16 * kk + (lmat & 1) * 8);
+                mma16816(s[j], qf[kk], b[0], b[1]);
+                mma16816(s[j + 1], qf[kk], b[2], b[3]);
+            }
+        }
+    }
+}
+
+// Masking, the running softmax in float32 (log2 domain; ``scale`` holds log2 e) and O += P V for one block.
+// pos_r: the position of the lane's two rows (g and g + 8), -1 for a row that does not exist.
+template <int VMAX, int NB>
+__device__ __forceinline__ void wa_softmax_pv(float (&s)[NB / 8][4], const bf16* vs, int strv, int nv8, int key0,
+                                              const int (&pos_r)[2], int window, int keep, bool masked, float scale,
+                                              WaState<VMAX>& st, int lane) {
+    const int t = lane & 3;
+    const int lrow = lane & 7, lmat = lane >> 3;
+    float mx[2] = {-INFINITY, -INFINITY};
+    if (masked) {
+#pragma unroll
+        for (int j = 0; j < NB / 8; ++j)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int r = e >> 1;
+                const int key = key0 + 8 * j + 2 * t + (e & 1);
+                const int p = pos_r[r];
+                const bool seen = key <= p && (window <= 0 || key > p - window || key < keep);
+                if (!seen) s[j][e] = -INFINITY;
+                mx[r] = fmaxf(mx[r], s[j][e]);
+            }
+    } else {
+#pragma unroll
+        for (int j = 0; j < NB / 8; ++j) {
+            mx[0] = fmaxf(mx[0], fmaxf(s[j][0], s[j][1]));
+            mx[1] = fmaxf(mx[1], fmaxf(s[j][2], s[j][3]));
+        }
+    }
+    float corr[2], msafe[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+        const float m_new = fmaxf(st.m[r], mx[r] * scale);
+        corr[r] = (m_new == -INFINITY) ? 1.f : exp2f(st.m[r] - m_new);
+        msafe[r] = (m_new == -INFINITY) ? 0.f : m_new;
+        st.m[r] = m_new;
+    }
+    float rs[2] = {0.f, 0.f};
+#pragma unroll
+    for (int j = 0; j < NB / 8; ++j)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int r = e >> 1;
+            const float p = exp2f(fmaf(s[j][e], scale, -msafe[r]));          // 2^(-inf) = 0 for hidden keys
+            s[j][e] = p;
+            rs[r] += p;
+        }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        rs[r] += __shfl_xor_sync(0xffffffffu, rs[r], 1);
+        rs[r] += __shfl_xor_sync(0xffffffffu, rs[r], 2);
+        st.l[r] = st.l[r] * corr[r] + rs[r];
+    }
+#pragma unroll
+    for (int i = 0; i < VMAX / 8; ++i) {
+        st.o[i][0] *= corr[0]; st.o[i][1] *= corr[0];
+        st.o[i][2] *= corr[1]; st.o[i][3] *= corr[1];
+    }
+    // O += P V.  A weight p goes in as hi + lo, hi = bf16(p), lo = bf16(p - hi): 16 bits of it reach the sum.
+#pragma unroll
+    for (int kk = 0; kk < NB / 16; ++kk) {
+        unsigned hi[4], lo[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const float a = s[2 * kk + (q >> 1)][(q & 1) * 2], b = s[2 * kk + (q >> 1)][(q & 1) * 2 + 1];
+            const __nv_bfloat162 h2 = __floats2bfloat162_rn(a, b);
+            const float2 hf = __bfloat1622float2(h2);
+            hi[q] = *reinterpret_cast<const unsigned*>(&h2);
+            lo[q] = pack_bf16(a - hf.x, b - hf.y);
+        }
+#pragma unroll
+        for (int i = 0; i < VMAX / 8; i += 2) {
+            if (i < nv8) {
+                // matrices: (keys 16kk.., entries 8i..), (keys 16kk+8.., 8i..), (keys 16kk.., 8i+8..), (.., +8)
+                unsigned b[4];
+                ldmatrix_x4_trans(b, vs + (16 * kk + (lmat & 1) * 8 + lrow) * strv + 8 * i + (lmat >> 1) * 8);
+                mma16816(st.o[i], hi, b[0], b[1]);
+                mma16816(st.o[i], lo, b[0], b[1]);
+                mma16816(st.o[i + 1], hi, b[2], b[3]);
+                mma16816(st.o[i + 1], lo, b[2], b[3]);
+            }
+        }
+    }
+}
+
+// The A fragments of one 16-row query tile straight from global memory: row_ptr[r] points at the head's
+// entries of the lane's row r (g or g + 8), or is null for a row that does not exist.
+template <int KMAX>
+__device__ __forceinline__ void wa_load_q(unsigned (&qf)[KMAX / 16][4], const bf16* const (&row_ptr)[2], int nk16, int lane) {
+    const int t = lane & 3;
+#pragma unroll
+    for (int kk = 0; kk < KMAX / 16; ++kk)
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const bf16* rp = row_ptr[q & 1];
+            qf[kk][q] = (kk < nk16 && rp != nullptr) ? *reinterpret_cast<const unsigned*>(rp + 16 * kk + (q >> 1) * 8 + 2 * t) : 0u;
+        }
+}
+
+// Visible blocks of NB keys for queries at positions p_lo..p_hi: first those that hold kept first positions
+// and lie below the window's first block, then the window's blocks.  Block i of the list:
+__device__ __forceinline__ int wa_block_of(int i, int n_kept, int first_win) { return i < n_kept ? i : first_win + (i - n_kept); }
+
+template <int KMAX, int VMAX>
+__global__ void __launch_bounds__(256) window_attention_prefill_kernel(
+    const bf16* proj, int ld, int off_g, bf16* out, const int* __restrict__ tiles, const bf16* k_pages, const bf16* v_pages,
+    const int* __restrict__ table, int max_blocks, int bs, int nq, int nkv, int dk, int dv, float scale, int window, int keep) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    pdl_trigger();
+    const int* tl = tiles + 4 * blockIdx.x;
+    const int row0 = tl[0], n_rows = tl[1], slot = tl[2], p0 = tl[3];
+    pdl_wait();
+    if (n_rows <= 0 || slot < 0) return;                      // an empty tile of a bucketed list
+    const int h = blockIdx.y, kvh = h / (nq / nkv);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+    const int strk = dk + 8, strv = dv + 8, nk16 = dk >> 4, nv8 = dv >> 3;
+    bf16* ksm = reinterpret_cast<bf16*>(smem_raw);                        // [2][64][strk]
+    bf16* vsm = ksm + 2 * WA_PF_KEYS * strk;                              // [2][64][strv]
+    const int* trow = table + (size_t)slot * max_blocks;
+    const int p_hi = p0 + n_rows - 1;
+    const int lo_tile = window > 0 ? max(0, p0 - window + 1) : 0;
+    const int first_win = lo_tile / WA_PF_KEYS, last_win = p_hi / WA_PF_KEYS;
+    const int n_kept = min((min(keep, lo_tile) + WA_PF_KEYS - 1) / WA_PF_KEYS, first_win);
+    const int nb = n_kept + last_win - first_win + 1;
+    // the warp's rows
+    int pos_r[2];
+    const bf16* qrow[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int lr = warp * 16 + g + 8 * r;
+        pos_r[r] = lr < n_rows ? p0 + lr : -1;
+        qrow[r] = lr < n_rows ? proj + (size_t)(row0 + lr) * ld + (size_t)h * dk : nullptr;
+    }
+    unsigned qf[KMAX / 16][4];
+    wa_load_q<KMAX>(qf, qrow, nk16, lane);
+    const bool warp_live = warp * 16 < n_rows;
+    const int wp_lo = p0 + warp * 16, wp_hi = min(p0 + warp * 16 + 15, p_hi);     // positions of the warp's rows
+    WaState<VMAX> st;
+    st.init();
+    auto load = [&](int i, int stage) {
+        const int key0 = wa_block_of(i, n_kept, first_win) * WA_PF_KEYS;
+        wa_gather<WA_PF_KEYS, 256>(ksm + stage * WA_PF_KEYS * strk, strk, k_pages, trow, key0, p_hi, bs, nkv, kvh, dk, tid);
+        wa_gather<WA_PF_KEYS, 256>(vsm + stage * WA_PF_KEYS * strv, strv, v_pages, trow, key0, p_hi, bs, nkv, kvh, dv, tid);
+        __pipeline_commit();
+    };
+    load(0, 0);
+    for (int i = 0; i < nb; ++i) {
+        if (i + 1 < nb) load(i + 1, (i + 1) & 1);
+        else __pipeline_commit();
+        __pipeline_wait_prior(1);
+        __syncthreads();
+        const int key0 = wa_block_of(i, n_kept, first_win) * WA_PF_KEYS;
+        // the warp skips a block none of its rows sees; it masks only at an edge of some row's visibility
+        const bool any = key0 <= wp_hi && (window <= 0 || key0 + WA_PF_KEYS - 1 > wp_lo - window || key0 < keep);
+        if (warp_live && any) {
+            const bool inner = key0 + WA_PF_KEYS - 1 <= wp_lo && warp * 16 + 15 < n_rows &&
+                               (window <= 0 || key0 > wp_hi - window || key0 + WA_PF_KEYS - 1 < keep);
+            float s[WA_PF_KEYS / 8][4];
+            wa_scores<KMAX, WA_PF_KEYS>(qf, ksm + (i & 1) * WA_PF_KEYS * strk, strk, nk16, lane, s);
+            wa_softmax_pv<VMAX, WA_PF_KEYS>(s, vsm + (i & 1) * WA_PF_KEYS * strv, strv, nv8, key0, pos_r, window, keep, !inner,
+                                            scale, st, lane);
+        }
+        __syncthreads();
+    }
+    __pipeline_wait_prior(0);
+    // epilogue: 1 / l, the head's gate, bfloat16
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int lr = warp * 16 + g + 8 * r;
+        if (lr >= n_rows) continue;
+        float f = st.l[r] > 0.f ? 1.f / st.l[r] : 0.f;
+        if (off_g >= 0) f *= 1.f / (1.f + expf(-to_f32(proj[(size_t)(row0 + lr) * ld + off_g + h])));
+        bf16* o = out + ((size_t)(row0 + lr) * nq + h) * dv;
+#pragma unroll
+        for (int i = 0; i < VMAX / 8; ++i)
+            if (i < nv8)
+                *reinterpret_cast<unsigned*>(o + 8 * i + 2 * t) = pack_bf16(st.o[i][2 * r] * f, st.o[i][2 * r + 1] * f);
+    }
+}
+
+template <int KMAX, int VMAX>
+__global__ void __launch_bounds__(WA_DEC_WARPS * 32) window_attention_decode_kernel(
+    const bf16* proj, int ld, int off_g, bf16* out, const int* rows, const int* positions, const int* row_slot,
+    const bf16* k_pages, const bf16* v_pages, const int* __restrict__ table, int max_blocks, int bs, int nq, int nkv, int dk,
+    int dv, float scale, int window, int keep) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    pdl_trigger();
+    const int row = rows[blockIdx.x];                        // inputs of the step: read before the wait
+    const int slot = row_slot[row];
+    const int pos = positions[row];
+    pdl_wait();
+    const int kvh = blockIdx.y, G = nq / nkv;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+    if (slot < 0) {                                          // a padding row of a graph bucket
+        for (int i = tid; i < G * dv; i += blockDim.x) out[((size_t)row * nq + (size_t)kvh * G) * dv + i] = __float2bfloat16_rn(0.f);
+        return;
+    }
+    const int strk = dk + 8, strv = dv + 8, nk16 = dk >> 4, nv8 = dv >> 3;
+    bf16* ksm = reinterpret_cast<bf16*>(smem_raw) + (size_t)warp * WA_DEC_KEYS * (strk + strv);
+    bf16* vsm = ksm + WA_DEC_KEYS * strk;
+    const int* trow = table + (size_t)slot * max_blocks;
+    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    const int first_win = lo / WA_DEC_KEYS, last_win = pos / WA_DEC_KEYS;
+    const int n_kept = min((min(keep, lo) + WA_DEC_KEYS - 1) / WA_DEC_KEYS, first_win);
+    const int nb = n_kept + last_win - first_win + 1;
+    // the tile's rows are the query heads of this kv head
+    int pos_r[2];
+    const bf16* qrow[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int hr = g + 8 * r;
+        pos_r[r] = hr < G ? pos : -1;
+        qrow[r] = hr < G ? proj + (size_t)row * ld + (size_t)(kvh * G + hr) * dk : nullptr;
+    }
+    unsigned qf[KMAX / 16][4];
+    wa_load_q<KMAX>(qf, qrow, nk16, lane);
+    WaState<VMAX> st;
+    st.init();
+    for (int i = warp; i < nb; i += WA_DEC_WARPS) {
+        const int key0 = wa_block_of(i, n_kept, first_win) * WA_DEC_KEYS;
+        wa_gather<WA_DEC_KEYS, 32>(ksm, strk, k_pages, trow, key0, pos, bs, nkv, kvh, dk, lane);
+        __pipeline_commit();
+        wa_gather<WA_DEC_KEYS, 32>(vsm, strv, v_pages, trow, key0, pos, bs, nkv, kvh, dv, lane);
+        __pipeline_commit();
+        __pipeline_wait_prior(1);                           // the keys are there, the values still on their way
+        __syncwarp();
+        float s[WA_DEC_KEYS / 8][4];
+        wa_scores<KMAX, WA_DEC_KEYS>(qf, ksm, strk, nk16, lane, s);
+        __pipeline_wait_prior(0);
+        __syncwarp();
+        const bool inner = key0 + WA_DEC_KEYS - 1 <= pos && G == 16 &&
+                           (window <= 0 || key0 > pos - window || key0 + WA_DEC_KEYS - 1 < keep);
+        wa_softmax_pv<VMAX, WA_DEC_KEYS>(s, vsm, strv, nv8, key0, pos_r, window, keep, !inner, scale, st, lane);
+        __syncwarp();                                        // the tile is free for the next block's copies
+    }
+    // merge the warps' partial results in warp order through shared memory (over the tiles, which are done)
+    __syncthreads();
+    float* part = reinterpret_cast<float*>(smem_raw);                    // [warps][16][dv + 2]
+    const int pstr = dv + 2;
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        float* pr = part + ((size_t)warp * 16 + g + 8 * r) * pstr;
+#pragma unroll
+        for (int i = 0; i < VMAX / 8; ++i)
+            if (i < nv8) { pr[8 * i + 2 * t] = st.o[i][2 * r]; pr[8 * i + 2 * t + 1] = st.o[i][2 * r + 1]; }
+        if (t == 0) { pr[dv] = st.m[r]; pr[dv + 1] = st.l[r]; }
+    }
+    __syncthreads();
+    for (int i = tid; i < G * dv; i += blockDim.x) {
+        const int hr = i / dv, d = i - hr * dv;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < WA_DEC_WARPS; ++w) M = fmaxf(M, part[((size_t)w * 16 + hr) * pstr + dv]);
+        float num = 0.f, den = 0.f;
+#pragma unroll
+        for (int w = 0; w < WA_DEC_WARPS; ++w) {
+            const float* pr = part + ((size_t)w * 16 + hr) * pstr;
+            const float f = pr[dv] == -INFINITY ? 0.f : exp2f(pr[dv] - M);
+            num += pr[d] * f;
+            den += pr[dv + 1] * f;
+        }
+        float f = den > 0.f ? 1.f / den : 0.f;
+        const int h = kvh * G + hr;
+        if (off_g >= 0) f *= 1.f / (1.f + expf(-to_f32(proj[(size_t)row * ld + off_g + h])));
+        out[((size_t)row * nq + h) * dv + d] = __float2bfloat16_rn(num * f);
+    }
+}
+
+// bfloat16 on tensor cores.  rows [n_decode]: the step's rows that are single decoded tokens; tiles [n_tiles][4]:
+// [first row, rows, slot, position of the first row] of the portions' query tiles (empty tiles are skipped).
+// Takes dk, dv multiples of 16 up to 128, nq / nkv <= 16 and scale > 0; other sizes are refused.
+ZLLM_API int zllm_window_attention_bf16(const void* proj, int ld, int off_g, void* out, const int* rows, int n_decode,
+                                        const int* tiles, int n_tiles, const int* positions, const int* row_slot,
+                                        const void* k_pages, const void* v_pages, const int* table, int max_blocks, int bs,
+                                        int nq, int nkv, int dk, int dv, float scale, int window, int keep_first, void* stream) {
+    if (n_decode <= 0 && n_tiles <= 0) return 0;
+    if (dk <= 0 || dv <= 0 || (dk % 16) || (dv % 16) || dk > 128 || dv > 128 || nkv <= 0 || nq % nkv || nq / nkv > 16 ||
+        !(scale > 0.f) || keep_first < 0 || (ld % 2) || (off_g >= 0 && off_g + nq > ld) ||
+        (((uintptr_t)proj | (uintptr_t)out | (uintptr_t)k_pages | (uintptr_t)v_pages) & 15))
+        return ZLLM_ERR_UNSUPPORTED;
+    cudaStream_t s = (cudaStream_t)stream;
+    const float sc = scale * 1.4426950408889634f;
+    const size_t pf_smem = (size_t)2 * WA_PF_KEYS * ((dk + 8) + (dv + 8)) * sizeof(bf16);
+    const size_t tiles_b = (size_t)WA_DEC_WARPS * WA_DEC_KEYS * ((dk + 8) + (dv + 8)) * sizeof(bf16);
+    const size_t merge_b = (size_t)WA_DEC_WARPS * 16 * (dv + 2) * sizeof(float);
+    const size_t dec_smem = tiles_b > merge_b ? tiles_b : merge_b;
+    static bool raised = false;
+    if (!raised) {
+        const int most = 2 * WA_PF_KEYS * (136 + 136) * (int)sizeof(bf16);
+        cudaError_t e = cudaSuccess;
+#define WA_ATTR(KM, VM) \
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(window_attention_prefill_kernel<KM, VM>, cudaFuncAttributeMaxDynamicSharedMemorySize, most); \
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(window_attention_decode_kernel<KM, VM>, cudaFuncAttributeMaxDynamicSharedMemorySize, most);
+        WA_ATTR(64, 64) WA_ATTR(64, 128) WA_ATTR(128, 64) WA_ATTR(128, 128)
+#undef WA_ATTR
+        if (e != cudaSuccess) return (int)e;
+        raised = true;
+    }
+    int rc = 0;
+#define WA_GO(KM, VM) do { \
+        if (n_decode > 0) \
+            rc = launch_pdl(window_attention_decode_kernel<KM, VM>, dim3(n_decode, nkv), dim3(WA_DEC_WARPS * 32), dec_smem, s, \
+                            (const bf16*)proj, ld, off_g, (bf16*)out, rows, positions, row_slot, (const bf16*)k_pages, \
+                            (const bf16*)v_pages, table, max_blocks, bs, nq, nkv, dk, dv, sc, window, keep_first); \
+        if (rc == 0 && n_tiles > 0) \
+            rc = launch_pdl(window_attention_prefill_kernel<KM, VM>, dim3(n_tiles, nq), dim3(256), pf_smem, s, (const bf16*)proj, \
+                            ld, off_g, (bf16*)out, tiles, (const bf16*)k_pages, (const bf16*)v_pages, table, max_blocks, bs, nq, \
+                            nkv, dk, dv, sc, window, keep_first); \
+        return rc; } while (0)
+    if (dk <= 64 && dv <= 64) WA_GO(64, 64);
+    if (dk <= 64) WA_GO(64, 128);
+    if (dv <= 64) WA_GO(128, 64);
+    WA_GO(128, 128);
+#undef WA_GO
 }

@@ -776,6 +776,22 @@ class CudaOps:
         self._check_window_cache(cache, nkv, dk, dv, proj.dtype, "window_attention")
         if tuple(out.shape) != (T, nq * dv) or out.dtype != proj.dtype or nq * dk > ld:
             raise BackendError("window_attention: output does not match")
+        G = nq // nkv
+        if proj.dtype == torch.bfloat16 and self.dtype == torch.bfloat16 and dk % 16 == 0 and dv % 16 == 0 and max(dk, dv) <= 128 \
+                and G <= 16 and scale > 0 and ld % 8 == 0 and (proj.data_ptr() | out.data_ptr()) & 15 == 0 \
+                and os.environ.get("ZLLM_WINDOW_ATTENTION_PLAIN", "") in ("", "0"):
+            # tensor cores: decoded rows with the group's heads as the tile's rows, portions by query tiles
+            tiles = ctx.aux.get("query_tiles") if ctx.aux else None
+            n_tiles = tiles.shape[0] if tiles is not None else 0
+            code = self.lib("attention_window").zllm_window_attention_bf16(
+                _ptr(proj), c_int(ld), c_int(off_g), _ptr(out), _ptr(ctx.decode_rows), c_int(ctx.n_decode), _ptr(tiles),
+                c_int(n_tiles), _ptr(ctx.positions), _ptr(ctx.row_slot), _ptr(cache.k_pages), _ptr(cache.v_pages),
+                _ptr(cache.block_table), c_int(cache.block_table.shape[1]), c_int(cache.block_size), c_int(nq), c_int(nkv),
+                c_int(dk), c_int(dv), c_float(scale), c_int(window or 0), c_int(keep_first or 0), self._stream())
+            self._check(code, "window_attention_bf16")
+            if ctx.n_decode > 0 and n_tiles > 0:
+                self.launches += 1
+            return
         code = self.lib("attention_window").zllm_window_attention_plain(
             _ptr(proj), c_int(ld), c_int(off_g), _ptr(out), _ptr(ctx.positions), _ptr(ctx.row_slot), _ptr(cache.k_pages),
             _ptr(cache.v_pages), _ptr(cache.block_table), c_int(cache.block_table.shape[1]), c_int(cache.block_size), c_int(T),

@@ -33,6 +33,9 @@ class RoutedExperts(FeedForward):
     capturable = True
     can_overwrite = True
     KERNELS = ("moe", "gemm_grouped")
+    # a list, when somebody wants to know what was chosen: every call then appends (slots of the rows, their
+    # positions, the chosen experts [rows, top]) as copies on the device.  Only outside captured graphs.
+    record = None
 
     def __init__(self, hidden_size: int, expert_size: int, n_experts: int, top: int, n_groups: int = 1,
                  keep_groups: int = 1, residual_scale: float = 1.0, init_std: float = 0.02, score: str = "softmax",
@@ -115,6 +118,8 @@ class RoutedExperts(FeedForward):
         wts = ctx.ws.get("moe_weight", (T, cols), torch.float32)
         ops.moe_route(h, self.w_router, self.top, self.n_groups, self.keep_groups, idx, wts, score=self.score,
                       normalise=self.normalise, n_shared=self.n_shared, shared_gate=self.shared_gate)
+        if self.record is not None:
+            self.record.append((ctx.row_slot.clone(), ctx.positions.clone(), idx[:, :self.top].clone()))
         ops.moe_experts(h, idx, wts, self.w_gate, self.w_up, self.w_down, residual, self.residual_scale, ctx.ws,
                         n_input_weighted=self.top if self.weight_on == "input" else 0, activation=self.activation,
                         accumulate=accumulate)
