@@ -223,23 +223,47 @@ struct WaState {
     }
 };
 
-// NK rows of keys or values (keys key0 .. key0 + NK - 1 of one request and kv head) into a shared tile
-// [NK][str] by 16-byte async copies of NTHR threads; rows beyond ``key_hi`` or without a page become zeros.
-template <int NK, int NTHR>
-__device__ __forceinline__ void wa_gather(bf16* tile, int str, const bf16* pages, const int* __restrict__ trow, int key0,
-                                          int key_hi, int bs, int nkv, int kvh, int d, int tid) {
+// Where key ``key`` of the request lies in the pools: (page * nkv + kvh) * bs + position in the page, or -1 when
+// the key is beyond ``key_hi`` or its page has gone back to the pool.
+__device__ __forceinline__ long long wa_locate(const int* __restrict__ trow, int key, int key_hi, int bs, int nkv, int kvh) {
+    if (key > key_hi) return -1;
+    const int blk = key / bs;
+    const int page = trow[blk];
+    return page >= 0 ? ((long long)page * nkv + kvh) * bs + (key - blk * bs) : -1;
+}
+
+// A block of 64 keys and their values into shared tiles [64][str] by 256 threads: four threads per row, ONE table
+// lookup per thread (the row's place serves its key and its value), then independent 16-byte async copies;
+// a row without a page becomes zeros.
+__device__ __forceinline__ void wa_gather_block64(bf16* ktile, int strk, bf16* vtile, int strv, const bf16* k_pages,
+                                                  const bf16* v_pages, const int* __restrict__ trow, int key0, int key_hi,
+                                                  int bs, int nkv, int kvh, int dk, int dv, int tid) {
+    const int r = tid >> 2, part = tid & 3;
+    const long long at = wa_locate(trow, key0 + r, key_hi, bs, nkv, kvh);
+    bf16* kd = ktile + r * strk;
+    bf16* vd = vtile + r * strv;
+    if (at >= 0) {
+        const bf16* ks = k_pages + at * dk;
+        const bf16* vs = v_pages + at * dv;
+        for (int c = part; c < (dk >> 3); c += 4) __pipeline_memcpy_async(kd + c * 8, ks + c * 8, 16);
+        for (int c = part; c < (dv >> 3); c += 4) __pipeline_memcpy_async(vd + c * 8, vs + c * 8, 16);
+    } else {
+        for (int c = part; c < (dk >> 3); c += 4) *reinterpret_cast<uint4*>(kd + c * 8) = make_uint4(0, 0, 0, 0);
+        for (int c = part; c < (dv >> 3); c += 4) *reinterpret_cast<uint4*>(vd + c * 8) = make_uint4(0, 0, 0, 0);
+    }
+}
+
+// 32 rows of keys OR values by one warp: lane r has looked up row r's place (``at``); the lanes then walk the
+// rows' 16-byte pieces in order (consecutive lanes, consecutive pieces of a row), each fetching the place of its
+// piece's row from the lane that holds it.
+__device__ __forceinline__ void wa_gather_rows32(bf16* tile, int str, const bf16* pages, long long at, int d, int lane) {
     const int chunks = d >> 3;
-    for (int c = tid; c < NK * chunks; c += NTHR) {
+    for (int it = 0; it < chunks; ++it) {                    // 32 * chunks pieces, 32 per pass
+        const int c = lane + 32 * it;
         const int r = c / chunks, ch = c - r * chunks;
-        const int key = key0 + r;
+        const long long a = __shfl_sync(0xffffffffu, at, r);
         bf16* dst = tile + r * str + ch * 8;
-        const bf16* src = nullptr;
-        if (key <= key_hi) {
-            const int blk = key / bs;
-            const int page = trow[blk];
-            if (page >= 0) src = pages + (((size_t)page * nkv + kvh) * bs + (key - blk * bs)) * d + ch * 8;
-        }
-        if (src != nullptr) __pipeline_memcpy_async(dst, src, 16);
+        if (a >= 0) __pipeline_memcpy_async(dst, pages + a * d + ch * 8, 16);
         else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
     }
 }
@@ -300,7 +324,7 @@ __device__ __forceinline__ void wa_softmax_pv(float (&s)[NB / 8][4], const bf16*
         mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
         mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
         const float m_new = fmaxf(st.m[r], mx[r] * scale);
-        corr[r] = (m_new == -INFINITY) ? 1.f : exp2f(st.m[r] - m_new);
+        corr[r] = (m_new == -INFINITY) ? 1.f : ex2_approx(st.m[r] - m_new);
         msafe[r] = (m_new == -INFINITY) ? 0.f : m_new;
         st.m[r] = m_new;
     }
@@ -310,7 +334,7 @@ __device__ __forceinline__ void wa_softmax_pv(float (&s)[NB / 8][4], const bf16*
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
             const int r = e >> 1;
-            const float p = exp2f(fmaf(s[j][e], scale, -msafe[r]));          // 2^(-inf) = 0 for hidden keys
+            const float p = ex2_approx(fmaf(s[j][e], scale, -msafe[r]));     // 2^(-inf) = 0 for hidden keys
             s[j][e] = p;
             rs[r] += p;
         }
@@ -408,8 +432,8 @@ __global__ void __launch_bounds__(256) window_attention_prefill_kernel(
     st.init();
     auto load = [&](int i, int stage) {
         const int key0 = wa_block_of(i, n_kept, first_win) * WA_PF_KEYS;
-        wa_gather<WA_PF_KEYS, 256>(ksm + stage * WA_PF_KEYS * strk, strk, k_pages, trow, key0, p_hi, bs, nkv, kvh, dk, tid);
-        wa_gather<WA_PF_KEYS, 256>(vsm + stage * WA_PF_KEYS * strv, strv, v_pages, trow, key0, p_hi, bs, nkv, kvh, dv, tid);
+        wa_gather_block64(ksm + stage * WA_PF_KEYS * strk, strk, vsm + stage * WA_PF_KEYS * strv, strv, k_pages, v_pages, trow,
+                          key0, p_hi, bs, nkv, kvh, dk, dv, tid);
         __pipeline_commit();
     };
     load(0, 0);
@@ -465,8 +489,9 @@ __global__ void __launch_bounds__(WA_DEC_WARPS * 32) window_attention_decode_ker
         return;
     }
     const int strk = dk + 8, strv = dv + 8, nk16 = dk >> 4, nv8 = dv >> 3;
-    bf16* ksm = reinterpret_cast<bf16*>(smem_raw) + (size_t)warp * WA_DEC_KEYS * (strk + strv);
-    bf16* vsm = ksm + WA_DEC_KEYS * strk;
+    // per warp two stages of [32][strk] keys + [32][strv] values: the next block's rows are on their way while
+    // this one's are multiplied
+    bf16* wsm = reinterpret_cast<bf16*>(smem_raw) + (size_t)warp * 2 * WA_DEC_KEYS * (strk + strv);
     const int* trow = table + (size_t)slot * max_blocks;
     const int lo = window > 0 ? max(0, pos - window + 1) : 0;
     const int first_win = lo / WA_DEC_KEYS, last_win = pos / WA_DEC_KEYS;
@@ -485,23 +510,36 @@ __global__ void __launch_bounds__(WA_DEC_WARPS * 32) window_attention_decode_ker
     wa_load_q<KMAX>(qf, qrow, nk16, lane);
     WaState<VMAX> st;
     st.init();
-    for (int i = warp; i < nb; i += WA_DEC_WARPS) {
+    auto issue = [&](int i, int stage) {                     // two copy groups per block: its keys, then its values
+        bf16* ksm = wsm + (size_t)stage * WA_DEC_KEYS * (strk + strv);
         const int key0 = wa_block_of(i, n_kept, first_win) * WA_DEC_KEYS;
-        wa_gather<WA_DEC_KEYS, 32>(ksm, strk, k_pages, trow, key0, pos, bs, nkv, kvh, dk, lane);
+        const long long at = wa_locate(trow, key0 + lane, pos, bs, nkv, kvh);
+        wa_gather_rows32(ksm, strk, k_pages, at, dk, lane);
         __pipeline_commit();
-        wa_gather<WA_DEC_KEYS, 32>(vsm, strv, v_pages, trow, key0, pos, bs, nkv, kvh, dv, lane);
+        wa_gather_rows32(ksm + WA_DEC_KEYS * strk, strv, v_pages, at, dv, lane);
         __pipeline_commit();
-        __pipeline_wait_prior(1);                           // the keys are there, the values still on their way
+    };
+    if (warp < nb) issue(warp, 0);
+    int n = 0;
+    for (int i = warp; i < nb; i += WA_DEC_WARPS, ++n) {
+        const int stage = n & 1;
+        if (i + WA_DEC_WARPS < nb) issue(i + WA_DEC_WARPS, stage ^ 1);
+        else { __pipeline_commit(); __pipeline_commit(); }
+        const bf16* ksm = wsm + (size_t)stage * WA_DEC_KEYS * (strk + strv);
+        const bf16* vsm = ksm + WA_DEC_KEYS * strk;
+        const int key0 = wa_block_of(i, n_kept, first_win) * WA_DEC_KEYS;
+        __pipeline_wait_prior(3);                           // this block's keys are there
         __syncwarp();
         float s[WA_DEC_KEYS / 8][4];
         wa_scores<KMAX, WA_DEC_KEYS>(qf, ksm, strk, nk16, lane, s);
-        __pipeline_wait_prior(0);
+        __pipeline_wait_prior(2);                           // and its values
         __syncwarp();
         const bool inner = key0 + WA_DEC_KEYS - 1 <= pos && G == 16 &&
                            (window <= 0 || key0 > pos - window || key0 + WA_DEC_KEYS - 1 < keep);
         wa_softmax_pv<VMAX, WA_DEC_KEYS>(s, vsm, strv, nv8, key0, pos_r, window, keep, !inner, scale, st, lane);
-        __syncwarp();                                        // the tile is free for the next block's copies
+        __syncwarp();                                        // the stage is free for the block after next
     }
+    __pipeline_wait_prior(0);
     // merge the warps' partial results in warp order through shared memory (over the tiles, which are done)
     __syncthreads();
     float* part = reinterpret_cast<float*>(smem_raw);                    // [warps][16][dv + 2]
@@ -550,12 +588,12 @@ ZLLM_API int zllm_window_attention_bf16(const void* proj, int ld, int off_g, voi
     cudaStream_t s = (cudaStream_t)stream;
     const float sc = scale * 1.4426950408889634f;
     const size_t pf_smem = (size_t)2 * WA_PF_KEYS * ((dk + 8) + (dv + 8)) * sizeof(bf16);
-    const size_t tiles_b = (size_t)WA_DEC_WARPS * WA_DEC_KEYS * ((dk + 8) + (dv + 8)) * sizeof(bf16);
+    const size_t tiles_b = (size_t)WA_DEC_WARPS * 2 * WA_DEC_KEYS * ((dk + 8) + (dv + 8)) * sizeof(bf16);
     const size_t merge_b = (size_t)WA_DEC_WARPS * 16 * (dv + 2) * sizeof(float);
     const size_t dec_smem = tiles_b > merge_b ? tiles_b : merge_b;
     static bool raised = false;
     if (!raised) {
-        const int most = 2 * WA_PF_KEYS * (136 + 136) * (int)sizeof(bf16);
+        const int most = WA_DEC_WARPS * 2 * WA_DEC_KEYS * (136 + 136) * (int)sizeof(bf16);     // >= the portions' two stages of 64
         cudaError_t e = cudaSuccess;
 #define WA_ATTR(KM, VM) \
         if (e == cudaSuccess) e = cudaFuncSetAttribute(window_attention_prefill_kernel<KM, VM>, cudaFuncAttributeMaxDynamicSharedMemorySize, most); \
