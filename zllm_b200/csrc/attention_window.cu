@@ -24,7 +24,7 @@
 // bfloat16 with key and value sizes that are multiples of 16 (up to 128) runs on tensor cores
 // (mma.sync m16n8k16, float32 scores, softmax and sums):
 //   prompt portions  one CTA per (tile of 128 query rows of a portion, query head), eight warps of 16
-//                    rows; keys and values come in blocks of 64 through a two-stage cp.async ring,
+//                    rows; keys and values come in blocks of 64 through a three-stage cp.async ring,
 //                    gathered through the block table; only the blocks that hold a kept first
 //                    position or a key of the tile's window are visited, and only blocks that touch
 //                    an edge of some row's visibility pay for the masking.
@@ -394,8 +394,9 @@ __device__ __forceinline__ void wa_load_q(unsigned (&qf)[KMAX / 16][4], const bf
 // and lie below the window's first block, then the window's blocks.  Block i of the list:
 __device__ __forceinline__ int wa_block_of(int i, int n_kept, int first_win) { return i < n_kept ? i : first_win + (i - n_kept); }
 
+#define WA_PF_STAGES 3
 template <int KMAX, int VMAX>
-__global__ void __launch_bounds__(256) window_attention_prefill_kernel(
+__global__ void __launch_bounds__(256, (KMAX + VMAX <= 128) ? 2 : 1) window_attention_prefill_kernel(
     const bf16* proj, int ld, int off_g, bf16* out, const int* __restrict__ tiles, const bf16* k_pages, const bf16* v_pages,
     const int* __restrict__ table, int max_blocks, int bs, int nq, int nkv, int dk, int dv, float scale, int window, int keep) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -407,8 +408,8 @@ __global__ void __launch_bounds__(256) window_attention_prefill_kernel(
     const int h = blockIdx.y, kvh = h / (nq / nkv);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
     const int strk = dk + 8, strv = dv + 8, nk16 = dk >> 4, nv8 = dv >> 3;
-    bf16* ksm = reinterpret_cast<bf16*>(smem_raw);                        // [2][64][strk]
-    bf16* vsm = ksm + 2 * WA_PF_KEYS * strk;                              // [2][64][strv]
+    bf16* ksm = reinterpret_cast<bf16*>(smem_raw);                        // [stages][64][strk]
+    bf16* vsm = ksm + WA_PF_STAGES * WA_PF_KEYS * strk;                   // [stages][64][strv]
     const int* trow = table + (size_t)slot * max_blocks;
     const int p_hi = p0 + n_rows - 1;
     const int lo_tile = window > 0 ? max(0, p0 - window + 1) : 0;
@@ -436,12 +437,17 @@ __global__ void __launch_bounds__(256) window_attention_prefill_kernel(
                           key0, p_hi, bs, nkv, kvh, dk, dv, tid);
         __pipeline_commit();
     };
+    // a ring of three stages, two blocks ahead, ONE barrier per block: the stage that block i + 2 is copied into
+    // was read last for block i - 1, which every warp has finished when it passes the barrier of block i
     load(0, 0);
+    if (nb > 1) load(1, 1);
+    else __pipeline_commit();
     for (int i = 0; i < nb; ++i) {
-        if (i + 1 < nb) load(i + 1, (i + 1) & 1);
-        else __pipeline_commit();
-        __pipeline_wait_prior(1);
+        __pipeline_wait_prior(1);                            // block i has landed (block i + 1 may still be on its way)
         __syncthreads();
+        if (i + 2 < nb) load(i + 2, (i + 2) % WA_PF_STAGES);
+        else __pipeline_commit();
+        const int stage = i % WA_PF_STAGES;
         const int key0 = wa_block_of(i, n_kept, first_win) * WA_PF_KEYS;
         // the warp skips a block none of its rows sees; it masks only at an edge of some row's visibility
         const bool any = key0 <= wp_hi && (window <= 0 || key0 + WA_PF_KEYS - 1 > wp_lo - window || key0 < keep);
@@ -449,11 +455,10 @@ __global__ void __launch_bounds__(256) window_attention_prefill_kernel(
             const bool inner = key0 + WA_PF_KEYS - 1 <= wp_lo && warp * 16 + 15 < n_rows &&
                                (window <= 0 || key0 > wp_hi - window || key0 + WA_PF_KEYS - 1 < keep);
             float s[WA_PF_KEYS / 8][4];
-            wa_scores<KMAX, WA_PF_KEYS>(qf, ksm + (i & 1) * WA_PF_KEYS * strk, strk, nk16, lane, s);
-            wa_softmax_pv<VMAX, WA_PF_KEYS>(s, vsm + (i & 1) * WA_PF_KEYS * strv, strv, nv8, key0, pos_r, window, keep, !inner,
+            wa_scores<KMAX, WA_PF_KEYS>(qf, ksm + stage * WA_PF_KEYS * strk, strk, nk16, lane, s);
+            wa_softmax_pv<VMAX, WA_PF_KEYS>(s, vsm + stage * WA_PF_KEYS * strv, strv, nv8, key0, pos_r, window, keep, !inner,
                                             scale, st, lane);
         }
-        __syncthreads();
     }
     __pipeline_wait_prior(0);
     // epilogue: 1 / l, the head's gate, bfloat16
@@ -587,13 +592,13 @@ ZLLM_API int zllm_window_attention_bf16(const void* proj, int ld, int off_g, voi
         return ZLLM_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
     const float sc = scale * 1.4426950408889634f;
-    const size_t pf_smem = (size_t)2 * WA_PF_KEYS * ((dk + 8) + (dv + 8)) * sizeof(bf16);
+    const size_t pf_smem = (size_t)WA_PF_STAGES * WA_PF_KEYS * ((dk + 8) + (dv + 8)) * sizeof(bf16);
     const size_t tiles_b = (size_t)WA_DEC_WARPS * 2 * WA_DEC_KEYS * ((dk + 8) + (dv + 8)) * sizeof(bf16);
     const size_t merge_b = (size_t)WA_DEC_WARPS * 16 * (dv + 2) * sizeof(float);
     const size_t dec_smem = tiles_b > merge_b ? tiles_b : merge_b;
     static bool raised = false;
     if (!raised) {
-        const int most = WA_DEC_WARPS * 2 * WA_DEC_KEYS * (136 + 136) * (int)sizeof(bf16);     // >= the portions' two stages of 64
+        const int most = WA_DEC_WARPS * 2 * WA_DEC_KEYS * (136 + 136) * (int)sizeof(bf16);     // >= the portions' three stages of 64
         cudaError_t e = cudaSuccess;
 #define WA_ATTR(KM, VM) \
         if (e == cudaSuccess) e = cudaFuncSetAttribute(window_attention_prefill_kernel<KM, VM>, cudaFuncAttributeMaxDynamicSharedMemorySize, most); \

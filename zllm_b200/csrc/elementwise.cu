@@ -150,10 +150,57 @@ __global__ void __launch_bounds__(256) rmsnorm_add_kernel(const float* y, const 
     }
 }
 
+// The same with 16-byte accesses and the row kept in registers (H % 4 == 0, H <= 256 * 4 * RV).
+template <typename WT, int RV>
+__global__ void __launch_bounds__(256) rmsnorm_add_vec_kernel(const float* y, const float* __restrict__ b, const WT* __restrict__ w,
+                                                              float* residual, int H, float eps) {
+    __shared__ float red[33];
+    pdl_trigger();
+    const int n4 = H >> 2;
+    float4 wv[RV], bv[RV];                               // weights and the bias: fetched before the wait
+#pragma unroll
+    for (int r = 0; r < RV; ++r) {
+        const int i = threadIdx.x + r * 256;
+        wv[r] = i < n4 ? make_float4(to_f32(w[4 * i]), to_f32(w[4 * i + 1]), to_f32(w[4 * i + 2]), to_f32(w[4 * i + 3]))
+                       : make_float4(0.f, 0.f, 0.f, 0.f);
+        bv[r] = (i < n4 && b != nullptr) ? reinterpret_cast<const float4*>(b)[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    pdl_wait();
+    const float4* yr = reinterpret_cast<const float4*>(y + (size_t)blockIdx.x * H);
+    float4* xr = reinterpret_cast<float4*>(residual + (size_t)blockIdx.x * H);
+    float4 v[RV];
+    float ss = 0.f;
+#pragma unroll
+    for (int r = 0; r < RV; ++r) {
+        const int i = threadIdx.x + r * 256;
+        v[r] = i < n4 ? yr[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+        v[r].x += bv[r].x; v[r].y += bv[r].y; v[r].z += bv[r].z; v[r].w += bv[r].w;
+        ss += v[r].x * v[r].x + v[r].y * v[r].y + v[r].z * v[r].z + v[r].w * v[r].w;
+    }
+    ss = block_sum(ss, red);
+    const float inv = rsqrtf(ss / (float)H + eps);
+#pragma unroll
+    for (int r = 0; r < RV; ++r) {
+        const int i = threadIdx.x + r * 256;
+        if (i >= n4) continue;
+        float4 x = xr[i];
+        x.x += v[r].x * inv * wv[r].x; x.y += v[r].y * inv * wv[r].y; x.z += v[r].z * inv * wv[r].z; x.w += v[r].w * inv * wv[r].w;
+        xr[i] = x;
+    }
+}
+
 ZLLM_API int zllm_rmsnorm_add(const float* y, const float* bias, const void* w, float* residual, int T, int H, float eps,
                               int w_bf16, void* stream) {
     if (T <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
+    const bool vec = H % 4 == 0 && (((uintptr_t)y | (uintptr_t)residual | (uintptr_t)bias) % 16 == 0);
+    if (vec && H <= 256 * 4 * 8) {
+        const bool small = H <= 256 * 4 * 2;
+        if (w_bf16 && small) return launch_pdl(rmsnorm_add_vec_kernel<bf16, 2>, dim3(T), dim3(256), 0, s, y, bias, (const bf16*)w, residual, H, eps);
+        if (w_bf16) return launch_pdl(rmsnorm_add_vec_kernel<bf16, 8>, dim3(T), dim3(256), 0, s, y, bias, (const bf16*)w, residual, H, eps);
+        if (small) return launch_pdl(rmsnorm_add_vec_kernel<float, 2>, dim3(T), dim3(256), 0, s, y, bias, (const float*)w, residual, H, eps);
+        return launch_pdl(rmsnorm_add_vec_kernel<float, 8>, dim3(T), dim3(256), 0, s, y, bias, (const float*)w, residual, H, eps);
+    }
     const int th = H >= 1024 ? 256 : 128;
     if (w_bf16) return launch_pdl(rmsnorm_add_kernel<bf16>, dim3(T), dim3(th), 0, s, y, bias, (const bf16*)w, residual, H, eps);
     return launch_pdl(rmsnorm_add_kernel<float>, dim3(T), dim3(th), 0, s, y, bias, (const float*)w, residual, H, eps);
@@ -190,12 +237,48 @@ __global__ void bias_silu_mul_kernel(const AT* gu, int ld, const float* __restri
     }
 }
 
+// bfloat16, I and ld multiples of 8, 16-byte aligned rows: eight outputs per thread with 16-byte accesses.
+__global__ void __launch_bounds__(256) bias_silu_mul_vec_kernel(const bf16* gu, int ld, const float* __restrict__ b, bf16* out, int I,
+                                                                size_t n8) {
+    pdl_trigger();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n8) { pdl_wait(); return; }
+    const int per_row = I >> 3;
+    const size_t t = i / (size_t)per_row;
+    const int j = (int)(i - t * (size_t)per_row) * 8;
+    float bg[8], bu[8];                                  // the biases are weights: fetched before the wait
+#pragma unroll
+    for (int e = 0; e < 8; e += 4) {
+        const float4 x = *reinterpret_cast<const float4*>(b + j + e), y = *reinterpret_cast<const float4*>(b + I + j + e);
+        bg[e] = x.x; bg[e + 1] = x.y; bg[e + 2] = x.z; bg[e + 3] = x.w;
+        bu[e] = y.x; bu[e + 1] = y.y; bu[e + 2] = y.z; bu[e + 3] = y.w;
+    }
+    pdl_wait();
+    const uint4 gr = *reinterpret_cast<const uint4*>(gu + t * ld + j), ur = *reinterpret_cast<const uint4*>(gu + t * ld + I + j);
+    const __nv_bfloat162* gp = reinterpret_cast<const __nv_bfloat162*>(&gr);
+    const __nv_bfloat162* up = reinterpret_cast<const __nv_bfloat162*>(&ur);
+    uint4 o;
+    unsigned* op = reinterpret_cast<unsigned*>(&o);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        const float2 g2 = __bfloat1622float2(gp[e]), u2 = __bfloat1622float2(up[e]);
+        const float g0 = g2.x + bg[2 * e], g1 = g2.y + bg[2 * e + 1];
+        const __nv_bfloat162 r = __floats2bfloat162_rn(g0 / (1.f + expf(-g0)) * (u2.x + bu[2 * e]),
+                                                       g1 / (1.f + expf(-g1)) * (u2.y + bu[2 * e + 1]));
+        op[e] = *reinterpret_cast<const unsigned*>(&r);
+    }
+    *reinterpret_cast<uint4*>(out + t * (size_t)I + j) = o;
+}
+
 ZLLM_API int zllm_bias_silu_mul(const void* gu, int ld, const float* b, void* out, int T, int I, int is_bf16, void* stream) {
     if (T <= 0 || I <= 0) return 0;
     if (ld < 2 * I) return ZLLM_ERR_UNSUPPORTED;
     const size_t n = (size_t)T * I;
-    const unsigned blocks = (unsigned)((n + 255) / 256);
     cudaStream_t s = (cudaStream_t)stream;
+    if (is_bf16 && I % 8 == 0 && ld % 8 == 0 && (((uintptr_t)gu | (uintptr_t)out) % 16 == 0) && ((uintptr_t)b % 16 == 0))
+        return launch_pdl(bias_silu_mul_vec_kernel, dim3((unsigned)((n / 8 + 255) / 256)), dim3(256), 0, s, (const bf16*)gu, ld, b,
+                          (bf16*)out, I, n / 8);
+    const unsigned blocks = (unsigned)((n + 255) / 256);
     if (is_bf16) return launch_pdl(bias_silu_mul_kernel<bf16>, dim3(blocks), dim3(256), 0, s, (const bf16*)gu, ld, b, (bf16*)out, I, n);
     return launch_pdl(bias_silu_mul_kernel<float>, dim3(blocks), dim3(256), 0, s, (const float*)gu, ld, b, (float*)out, I, n);
 }
