@@ -401,7 +401,9 @@ __global__ void __launch_bounds__(256, (KMAX + VMAX <= 128) ? 2 : 1) window_atte
     const int* __restrict__ table, int max_blocks, int bs, int nq, int nkv, int dk, int dv, float scale, int window, int keep) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     pdl_trigger();
-    const int* tl = tiles + 4 * blockIdx.x;
+    // the list runs from a portion's first tile to its last, and later tiles see more keys: the grid walks it
+    // backwards, so that the longest tiles start first and the short ones fill the tail
+    const int* tl = tiles + 4 * (gridDim.x - 1 - blockIdx.x);
     const int row0 = tl[0], n_rows = tl[1], slot = tl[2], p0 = tl[3];
     pdl_wait();
     if (n_rows <= 0 || slot < 0) return;                      // an empty tile of a bucketed list
