@@ -219,7 +219,7 @@ def test_experts_without_a_gate_matrix_weighted_on_their_input(ops, dtype, act, 
 @pytest.mark.parametrize("nq,nkv,dk,dv,dims,inter,bs,scaling", [
     (4, 2, 16, 24, 8, True, 16, {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 64}),
     (3, 3, 32, 16, 32, True, 8, None), (6, 1, 16, 16, 0, True, 4, None), (5, 5, 12, 18, 6, False, 4, None),
-    (8, 2, 64, 80, 16, True, 16, {"factor": 4.0, "low": 1.0, "high": 4.0, "original": 2048})])
+    (8, 2, 64, 96, 24, True, 16, {"factor": 6.0, "low": 1.0, "high": 8.0, "original": 512})])
 def test_rotation_and_cache_write(ops, dtype, nq, nkv, dk, dv, dims, inter, bs, scaling):
     from zllm_b200.cache import CacheManager
     from zllm_b200.parts import KVCacheSpec
@@ -324,7 +324,9 @@ def _attention_case(ops, dtype, nq, nkv, dk, dv, window, keep, bs, lens, spike=N
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("nq,nkv,dk,dv,window,keep,bs", [
     (4, 2, 16, 24, 24, 5, 16), (3, 3, 32, 16, 40, 0, 8), (6, 1, 16, 16, None, 0, 4), (3, 3, 24, 40, 7, 9, 8), (5, 5, 12, 18, 13, 3, 4),
-    (8, 2, 64, 32, 64, 16, 16), (4, 4, 64, 80, 96, 20, 16), (8, 1, 128, 128, 200, 4, 16), (2, 1, 96, 48, 33, 17, 32)])
+    (8, 2, 64, 32, 64, 16, 16), (6, 3, 48, 112, 70, 11, 16), (8, 1, 128, 128, 200, 4, 16), (2, 1, 96, 48, 33, 17, 32),
+    # sixteen heads on one key/value head fill the decode tile's rows (its unmasked path); seventeen go to the plain kernel
+    (16, 1, 32, 32, 48, 4, 16), (17, 1, 16, 16, 20, 3, 8)])
 def test_window_attention_in_prompts_portions_and_decoding(ops, dtype, nq, nkv, dk, dv, window, keep, bs):
     # whole prompts (one longer than several windows), portions with a cached prefix, single decoded tokens
     _attention_case(ops, dtype, nq, nkv, dk, dv, window, keep, bs, [(0, 150), (0, 3), (0, 1)])
