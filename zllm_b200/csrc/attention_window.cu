@@ -29,8 +29,8 @@
 //                    position or a key of the tile's window are visited, and only blocks that touch
 //                    an edge of some row's visibility pay for the masking.
 //   decoded rows     one CTA per (row, kv head); the query heads that share the kv head are the rows of
-//                    the tile, so keys and values are read once for the group; the four warps take the
-//                    visible blocks of 32 keys in turn, each with its own running maximum and sums,
+//                    the tile, so keys and values are read once for the group; the warps (eight, or four at the
+//                    largest sizes) take the visible blocks of 32 keys in turn, two stages each, with their own running maximum and sums,
 //                    and merge in warp order at the end.  A window bounds a row's keys, so there are no
 //                    splits over CTAs and no merge kernel.
 // The softmax weights stay 32-bit through the second product: a weight goes to the tensor cores as
@@ -478,8 +478,8 @@ __global__ void __launch_bounds__(256, (KMAX + VMAX <= 128) ? 2 : 1) window_atte
     }
 }
 
-template <int KMAX, int VMAX>
-__global__ void __launch_bounds__(WA_DEC_WARPS * 32) window_attention_decode_kernel(
+template <int KMAX, int VMAX, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32) window_attention_decode_kernel(
     const bf16* proj, int ld, int off_g, bf16* out, const int* rows, const int* positions, const int* row_slot,
     const bf16* k_pages, const bf16* v_pages, const int* __restrict__ table, int max_blocks, int bs, int nq, int nkv, int dk,
     int dv, float scale, int window, int keep) {
@@ -528,9 +528,9 @@ __global__ void __launch_bounds__(WA_DEC_WARPS * 32) window_attention_decode_ker
     };
     if (warp < nb) issue(warp, 0);
     int n = 0;
-    for (int i = warp; i < nb; i += WA_DEC_WARPS, ++n) {
+    for (int i = warp; i < nb; i += WARPS, ++n) {
         const int stage = n & 1;
-        if (i + WA_DEC_WARPS < nb) issue(i + WA_DEC_WARPS, stage ^ 1);
+        if (i + WARPS < nb) issue(i + WARPS, stage ^ 1);
         else { __pipeline_commit(); __pipeline_commit(); }
         const bf16* ksm = wsm + (size_t)stage * WA_DEC_KEYS * (strk + strv);
         const bf16* vsm = ksm + WA_DEC_KEYS * strk;
@@ -564,10 +564,10 @@ __global__ void __launch_bounds__(WA_DEC_WARPS * 32) window_attention_decode_ker
         const int hr = i / dv, d = i - hr * dv;
         float M = -INFINITY;
 #pragma unroll
-        for (int w = 0; w < WA_DEC_WARPS; ++w) M = fmaxf(M, part[((size_t)w * 16 + hr) * pstr + dv]);
+        for (int w = 0; w < WARPS; ++w) M = fmaxf(M, part[((size_t)w * 16 + hr) * pstr + dv]);
         float num = 0.f, den = 0.f;
 #pragma unroll
-        for (int w = 0; w < WA_DEC_WARPS; ++w) {
+        for (int w = 0; w < WARPS; ++w) {
             const float* pr = part + ((size_t)w * 16 + hr) * pstr;
             const float f = pr[dv] == -INFINITY ? 0.f : exp2f(pr[dv] - M);
             num += pr[d] * f;
@@ -595,16 +595,21 @@ ZLLM_API int zllm_window_attention_bf16(const void* proj, int ld, int off_g, voi
     cudaStream_t s = (cudaStream_t)stream;
     const float sc = scale * 1.4426950408889634f;
     const size_t pf_smem = (size_t)WA_PF_STAGES * WA_PF_KEYS * ((dk + 8) + (dv + 8)) * sizeof(bf16);
-    const size_t tiles_b = (size_t)WA_DEC_WARPS * 2 * WA_DEC_KEYS * ((dk + 8) + (dv + 8)) * sizeof(bf16);
-    const size_t merge_b = (size_t)WA_DEC_WARPS * 16 * (dv + 2) * sizeof(float);
+    // decoding: eight warps per CTA while their tiles fit into 160 KB, else four (the grid is only rows x kv heads,
+    // so the warps of a CTA are what keeps copies in flight)
+    const size_t warp_tiles = (size_t)2 * WA_DEC_KEYS * ((dk + 8) + (dv + 8)) * sizeof(bf16);
+    const int dec_warps = 8 * warp_tiles <= 160 * 1024 ? 8 : WA_DEC_WARPS;
+    const size_t tiles_b = dec_warps * warp_tiles;
+    const size_t merge_b = (size_t)dec_warps * 16 * (dv + 2) * sizeof(float);
     const size_t dec_smem = tiles_b > merge_b ? tiles_b : merge_b;
     static bool raised = false;
     if (!raised) {
-        const int most = WA_DEC_WARPS * 2 * WA_DEC_KEYS * (136 + 136) * (int)sizeof(bf16);     // >= the portions' three stages of 64
+        const int most = 160 * 1024;     // >= four warps' tiles at the largest sizes, eight warps' up to the limit above, the portions' three stages
         cudaError_t e = cudaSuccess;
 #define WA_ATTR(KM, VM) \
         if (e == cudaSuccess) e = cudaFuncSetAttribute(window_attention_prefill_kernel<KM, VM>, cudaFuncAttributeMaxDynamicSharedMemorySize, most); \
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(window_attention_decode_kernel<KM, VM>, cudaFuncAttributeMaxDynamicSharedMemorySize, most);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(window_attention_decode_kernel<KM, VM, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, most); \
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(window_attention_decode_kernel<KM, VM, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, most);
         WA_ATTR(64, 64) WA_ATTR(64, 128) WA_ATTR(128, 64) WA_ATTR(128, 128)
 #undef WA_ATTR
         if (e != cudaSuccess) return (int)e;
@@ -612,8 +617,12 @@ ZLLM_API int zllm_window_attention_bf16(const void* proj, int ld, int off_g, voi
     }
     int rc = 0;
 #define WA_GO(KM, VM) do { \
-        if (n_decode > 0) \
-            rc = launch_pdl(window_attention_decode_kernel<KM, VM>, dim3(n_decode, nkv), dim3(WA_DEC_WARPS * 32), dec_smem, s, \
+        if (n_decode > 0 && dec_warps == 8) \
+            rc = launch_pdl(window_attention_decode_kernel<KM, VM, 8>, dim3(n_decode, nkv), dim3(256), dec_smem, s, \
+                            (const bf16*)proj, ld, off_g, (bf16*)out, rows, positions, row_slot, (const bf16*)k_pages, \
+                            (const bf16*)v_pages, table, max_blocks, bs, nq, nkv, dk, dv, sc, window, keep_first); \
+        else if (n_decode > 0) \
+            rc = launch_pdl(window_attention_decode_kernel<KM, VM, 4>, dim3(n_decode, nkv), dim3(128), dec_smem, s, \
                             (const bf16*)proj, ld, off_g, (bf16*)out, rows, positions, row_slot, (const bf16*)k_pages, \
                             (const bf16*)v_pages, table, max_blocks, bs, nq, nkv, dk, dv, sc, window, keep_first); \
         if (rc == 0 && n_tiles > 0) \
